@@ -1,0 +1,230 @@
+"""CUDA compression kernels against the CPU oracle and the reference's golden vectors (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import tq_oracle as O
+from turboquant.core import PolarQuantConfig, make_codebook, make_wht_matrix, polarquant_compress
+from turboquant.kernels import _native, packed_compress, paged_layout
+from turboquant.kernels.paged import CacheFormat, Codebooks, allocate_cache, compress_and_scatter
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _inputs(n, seed=0, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, 128, generator=g)
+    if outliers:
+        x[:, [3, 40, 77, 120]] *= 10.0
+    return x
+
+
+def _half_ulp_close(got_h: torch.Tensor, want_f32: np.ndarray, max_ulp=1):
+    """fp16 values within max_ulp units in the last place of the fp16 rounding of want."""
+    want_h = torch.from_numpy(want_f32.astype(np.float16))
+    a = got_h.cpu().view(torch.int16).to(torch.int32)
+    b = want_h.view(torch.int16).to(torch.int32)
+    return (a - b).abs().max().item() <= max_ulp
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_polarquant_prerotated_bit_exact_vs_golden(golden, bits):
+    """Identical fp32 rotated inputs -> indices and signs equal to the reference's own outputs."""
+    x = torch.from_numpy(golden["pq_x"]).to(DEV)
+    c, b = make_codebook(128, bits)
+    r = polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=bits, use_qjl=True), None)
+    p = f"pq_b{bits}_pre_"
+    idx = r["indices"].cpu().numpy()
+    ref_idx = golden[p + "indices"].astype(np.int64)
+    signs = (r["signs"].cpu().numpy() > 0)
+    ref_signs = np.unpackbits(golden[p + "signs"], axis=1, bitorder="little").astype(bool)
+    assert r["indices"].dtype == torch.int64
+    assert (idx != ref_idx).mean() <= 1e-4 and np.abs(idx - ref_idx).max() <= 1
+    assert (signs != ref_signs).mean() <= 1e-4
+    assert set(np.unique(r["signs"].cpu().numpy())) <= {-1.0, 1.0}
+    np.testing.assert_allclose(r["norms"].cpu().numpy(), golden[p + "norms"], rtol=3e-7)
+    np.testing.assert_allclose(r["rot_residual_norm"].cpu().numpy(), golden[p + "rnorm"], rtol=2e-5, atol=1e-7)
+    np.testing.assert_allclose(r["k_mse_rot"][:8].cpu().numpy(), golden[p + "k_mse_rot"], rtol=3e-7, atol=1e-9)
+    # the all-zero row: norm 0, ties at boundary 0 go to the lower centroid, every sign +
+    assert r["norms"][5] == 0 and (r["signs"][5] == 1).all()
+    assert (r["indices"][5] == (1 << bits) // 2 - 1).all()
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+def test_polarquant_rotated_vs_golden(golden, bits):
+    """In-kernel fast WHT instead of x @ H: at most 1e-4 of coordinates move, and only by one centroid."""
+    x = torch.from_numpy(golden["pq_x"]).to(DEV)
+    c, b = make_codebook(128, bits)
+    H = make_wht_matrix(128).to(DEV)
+    r = polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=bits), H)
+    p = f"pq_b{bits}_rot_"
+    idx = r["indices"].cpu().numpy()
+    ref_idx = golden[p + "indices"].astype(np.int64)
+    assert (idx != ref_idx).mean() <= 1e-4 and np.abs(idx - ref_idx).max() <= 1
+    ref_signs = np.unpackbits(golden[p + "signs"], axis=1, bitorder="little").astype(bool)
+    assert ((r["signs"].cpu().numpy() > 0) != ref_signs).mean() <= 1e-4
+    np.testing.assert_allclose(r["norms"].cpu().numpy(), golden[p + "norms"], rtol=2e-6)
+
+
+def test_polarquant_dict_contract():
+    c, b = make_codebook(128, 3)
+    x = _inputs(32).to(DEV)
+    r = polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=3, use_qjl=False), make_wht_matrix(128).to(DEV))
+    assert sorted(r) == ["indices", "k_mse_rot", "norms"]
+    x3 = _inputs(32).reshape(4, 8, 128).to(DEV)
+    r3 = polarquant_compress(x3, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=3), make_wht_matrix(128).to(DEV))
+    assert r3["indices"].shape == (4, 8, 128) and r3["k_mse_rot"].shape == (4, 8, 128) and r3["signs"].shape == (4, 8, 128)
+    assert r3["norms"].shape == (32,) and (r3["norms"] >= 0).all()
+    assert 0 <= r3["indices"].min() and r3["indices"].max() < 8
+    cos = torch.nn.functional.cosine_similarity(x3.reshape(-1, 128) @ make_wht_matrix(128).to(DEV), r3["k_mse_rot"].reshape(-1, 128), dim=-1)
+    assert cos.mean() > 0.95
+    with pytest.raises(ValueError):
+        polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=3), torch.eye(128, device=DEV))
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_compress_k_v_contiguous_vs_oracle(bits, dtype):
+    n = 4099                                   # ragged: not a multiple of the 4 vectors a CTA takes
+    x = _inputs(n, seed=bits).to(dtype)
+    c, b = make_codebook(128, bits)
+    H = make_wht_matrix(128)
+    xin = x.float().numpy()                    # the oracle sees the same rounded inputs
+    for rotate in (False, True):
+        rot = O.make_wht_matrix(128) if rotate else None
+        o_idx, o_sg, o_rn, o_n = O.compress_k_packed(xin, c.numpy(), b.numpy(), bits, rot, permuted=False)
+        o_sgp = O.permute_signs_for_chunked(o_sg)
+        PiT = H.to(DEV) if rotate else None
+        k_idx, k_sg, k_rn, k_n = packed_compress.compress_k(x.to(DEV), PiT, None, c.to(DEV), b.to(DEV))
+        _, k_sgp, _, _ = packed_compress.compress_k_permuted(x.to(DEV), PiT, None, c.to(DEV), b.to(DEV))
+        assert k_idx.dtype == torch.uint8 and k_idx.shape == (n, 16 * bits) and k_sg.shape == (n, 16)
+        assert k_rn.dtype == torch.float16 and k_n.dtype == torch.float16
+        got = packed_compress.unpack_indices(k_idx.cpu(), bits).numpy()
+        want = O.unpack_indices(o_idx, bits)
+        mism = (got != want)
+        assert mism.mean() <= (0.0 if not rotate else 1e-4) + 1e-4 and np.abs(got.astype(int) - want).max() <= 1
+        if not rotate:
+            assert mism.sum() <= 2                                   # exact ties only
+            assert (np.unpackbits(k_sg.cpu().numpy(), axis=1) != np.unpackbits(o_sg, axis=1)).mean() <= 1e-5
+            assert (np.unpackbits(k_sgp.cpu().numpy(), axis=1) != np.unpackbits(o_sgp, axis=1)).mean() <= 1e-5
+        else:
+            assert (np.unpackbits(k_sg.cpu().numpy(), axis=1) != np.unpackbits(o_sg, axis=1)).mean() <= 1e-4
+        # permuted output is the reference's permutation of the sequential one
+        assert torch.equal(packed_compress.permute_signs_for_chunked(k_sg.cpu()), k_sgp.cpu())
+        assert _half_ulp_close(k_n, o_n.astype(np.float32)) and _half_ulp_close(k_rn, o_rn.astype(np.float32))
+        v_idx, v_n = packed_compress.compress_v(x.to(DEV), PiT, c.to(DEV), b.to(DEV))
+        ov_idx, ov_n = O.compress_v_packed(xin, c.numpy(), b.numpy(), bits, rot)
+        gotv = packed_compress.unpack_indices(v_idx.cpu(), bits).numpy()
+        assert (gotv != O.unpack_indices(ov_idx, bits)).mean() <= 1e-4
+        assert torch.equal(v_idx, k_idx) and torch.equal(v_n, k_n)   # V is the K computation without the residual
+
+
+def test_compress_empty_and_single():
+    c, b = make_codebook(128, 3)
+    e = torch.empty(0, 128, device=DEV)
+    k_idx, k_sg, k_rn, k_n = packed_compress.compress_k(e, None, None, c.to(DEV), b.to(DEV))
+    assert k_idx.shape == (0, 48) and k_n.shape == (0,)
+    one = _inputs(1).to(DEV)
+    k_idx, _, _, k_n = packed_compress.compress_k(one, None, None, c.to(DEV), b.to(DEV))
+    r = O.polarquant_compress(one.cpu().numpy(), c.numpy(), b.numpy(), 3, True, None)
+    assert np.array_equal(packed_compress.unpack_indices(k_idx.cpu(), 3).numpy(), r["indices"])
+
+
+@pytest.mark.parametrize("fmt_name,block_size", [("turbo2", 16), ("turbo3", 16), ("turbo4", 16), ("turbo3", 32)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_compress_paged_fields_vs_oracle(fmt_name, block_size, dtype):
+    fmt = CacheFormat.named(fmt_name)
+    books = Codebooks(fmt, DEV)
+    T, Hkv, nb = 150, 3, 16
+    g = torch.Generator().manual_seed(7)
+    key = torch.randn(T, Hkv, 128, generator=g)
+    val = torch.randn(T, Hkv, 128, generator=g)
+    key[..., [3, 40, 77, 120]] *= 10
+    key, val = key.to(dtype), val.to(dtype)
+    slots = torch.randperm(nb * block_size, generator=g)[:T]
+    cache = allocate_cache(nb, block_size, Hkv, fmt, DEV)
+    cache.fill_(0xA5)                                                 # stale bytes must be fully overwritten
+    compress_and_scatter(key.to(DEV), val.to(DEV), cache, slots.to(DEV), books, block_size)
+    assert _native.read_status(DEV) == 0
+    f = paged_layout.unpack_cache(cache.cpu(), block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl)
+    blk, off = slots // block_size, slots % block_size
+    H = O.make_wht_matrix(128)
+    ok = O.polarquant_compress(key.float().numpy().reshape(-1, 128), books.kc.cpu().numpy(), books.kb.cpu().numpy(),
+                               fmt.k_bits, fmt.use_qjl, H)
+    ov = O.polarquant_compress(val.float().numpy().reshape(-1, 128), books.vc.cpu().numpy(), books.vb.cpu().numpy(),
+                               fmt.v_bits, False, H)
+    got_k = f["k_idx"][blk, off].numpy().reshape(-1, 128)
+    got_v = f["v_idx"][blk, off].numpy().reshape(-1, 128)
+    assert (got_k != ok["indices"]).mean() <= 1e-4 and (got_v != ov["indices"]).mean() <= 1e-4
+    assert _half_ulp_close(f["k_norm"][blk, off].reshape(-1), ok["norms"])
+    assert _half_ulp_close(f["v_norm"][blk, off].reshape(-1), ov["norms"])
+    if fmt.use_qjl:
+        got_s = f["k_signs"][blk, off].numpy().reshape(-1, 128)
+        assert (got_s != (ok["signs"] > 0)).mean() <= 1e-4
+        assert _half_ulp_close(f["k_rnorm"][blk, off].reshape(-1), ok["rot_residual_norm"])
+    # slots that were not written keep their old bytes
+    untouched = torch.ones(nb * block_size, dtype=torch.bool)
+    untouched[slots] = False
+    raw = paged_layout.unpack_cache(torch.full_like(cache.cpu(), 0xA5), block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl)
+    ub, uo = torch.nonzero(untouched).squeeze(1) // block_size, torch.nonzero(untouched).squeeze(1) % block_size
+    assert torch.equal(f["k_idx"][ub, uo], raw["k_idx"][ub, uo]) and torch.equal(f["v_idx"][ub, uo], raw["v_idx"][ub, uo])
+
+
+def test_compress_paged_prerotated_strided_and_bad_slots():
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    T, Hkv, nb, bs = 20, 2, 4, 16
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(T, 3 * Hkv, 128, generator=g).half().to(DEV)      # K and V as strided views of one buffer
+    key, val = qkv[:, Hkv:2 * Hkv], qkv[:, 2 * Hkv:]
+    slots = torch.arange(T, dtype=torch.int64)
+    slots[3] = -1                                                       # padding slot -> clamped to 0 (like the reference)
+    slots[0] = 5                                                        # so slot 0 is written by token 3 only
+    slots[7] = nb * bs + 3                                              # beyond the cache -> skipped and flagged
+    cache = allocate_cache(nb, bs, Hkv, fmt, DEV)
+    compress_and_scatter(key, val, cache, slots.to(DEV), books, bs, prerotated=True)
+    assert _native.read_status(DEV) == _native.STATUS_BAD_SLOT
+    f = paged_layout.unpack_cache(cache.cpu(), bs, 3, 3, True)
+    ok = O.polarquant_compress(key.float().cpu().numpy().reshape(-1, 128), books.kc.cpu().numpy(),
+                               books.kb.cpu().numpy(), 3, True, None)
+    want = ok["indices"].reshape(T, Hkv, 128)
+    assert np.array_equal(f["k_idx"][0, 0].numpy(), want[3])            # token 3 landed in slot 0
+    assert np.array_equal(f["k_idx"][0, 5].numpy(), want[0])
+    assert np.array_equal(f["k_idx"][0, 9].numpy(), want[9])
+    assert (f["k_idx"][0, 7] == 0).all()                                # token 7 was skipped; slot 7 untouched (zeros)
+    with pytest.raises(ValueError):
+        compress_and_scatter(key, val, cache[:, :, :-16], slots.to(DEV), books, bs)
+
+
+def test_wht_rows_matches_matrix():
+    x = _inputs(257, seed=5)
+    H = make_wht_matrix(128)
+    for dtype, tol in ((torch.float32, 2e-5), (torch.float16, 4e-2), (torch.bfloat16, 3e-1)):
+        xin = x.to(dtype)
+        y = _native.wht_rows(xin.to(DEV), 0.5)
+        assert y.dtype == dtype
+        ref = (xin.float() @ H) * 0.5
+        assert (y.float().cpu() - ref).abs().max() <= tol
+    y = _native.wht_rows(_native.wht_rows(x.to(DEV)))                  # H is its own inverse
+    assert (y.cpu() - x).abs().max() < 1e-4
+
+
+def test_full_size_properties():
+    """1M vectors: scale invariance of indices and signs, norm homogeneity, idempotent re-compression."""
+    n = 1 << 20
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(n, 128, generator=g, device=DEV, dtype=torch.float16)
+    c, b = make_codebook(128, 3)
+    H = make_wht_matrix(128).to(DEV)
+    i1, s1, rn1, n1 = packed_compress.compress_k(x, H, None, c.to(DEV), b.to(DEV))
+    i2, s2, rn2, n2 = packed_compress.compress_k(x * 2, H, None, c.to(DEV), b.to(DEV))   # exact power-of-two scaling
+    assert torch.equal(i1, i2) and torch.equal(s1, s2)
+    assert torch.equal(n2.float(), (n1.float() * 2)) and torch.equal(rn2.float(), rn1.float() * 2)
+    # index histogram is the Lloyd-Max cell mass of a Gaussian (all 8 cells used, symmetric)
+    idx = packed_compress.unpack_indices(i1[:65536].cpu(), 3).long()
+    hist = torch.bincount(idx.reshape(-1), minlength=8).float()
+    hist /= hist.sum()
+    assert (hist - hist.flip(0)).abs().max() < 2e-3 and hist.min() > 0.02
+    # checksum of checksums is reproducible run to run
+    assert torch.equal(i1.sum(dtype=torch.int64), packed_compress.compress_k(x, H, None, c.to(DEV), b.to(DEV))[0].sum(dtype=torch.int64))

@@ -1,0 +1,706 @@
+// Asymmetric packed paged decode attention (GQA, split-K, optional Sparse-V) for sm_100a.
+//
+// One CTA = 4 warps works on a chunk of 16-token pages of one (sequence, kv head,
+// group of <= 8 query heads).  Every warp owns every 4th page of the chunk and is
+// its own producer and consumer: lane 0 streams the next packed pages from HBM
+// into the warp's private shared-memory ring with bulk async copies that
+// complete on mbarriers, the whole warp then
+//   * turns packed indices into fp16 tensor-core fragments with byte-permute
+//     lookups (the codebook lives in four registers),
+//   * scores 16 tokens x 8 query heads with mma.m16n8k16 (tokens on M, the GQA
+//     group on N), a second MMA chain for the +-1 QJL sign term,
+//   * runs the online softmax on the accumulator fragment,
+//   * accumulates P V with mma (the transposed P fragment comes from one
+//     movmatrix per 8 tokens; the two dims a lane owns per column are told
+//     apart by the row half of the accumulator, so V is fed exactly as stored).
+// Warps merge in shared memory; chunks merge in a second small kernel.
+//
+// Arithmetic restated from the reference: score and softmax of
+// turboquant/kernels/packed_attention.py:150-196,273-284, paging and GQA head
+// mapping of turboquant/kernels/sparse_v.py:39-48,70-71, skip rule of
+// sparse_v.py:108-123,149.
+#include "tq_common.cuh"
+
+namespace tq {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kOPad = 132;  // row stride of the merge buffer (floats)
+constexpr int kStages = 4;  // pages in flight per warp
+constexpr int kBarBytes = kWarps * 2 * kStages * 8;  // mbarriers at the start of dynamic shared memory
+
+struct DecodeParams {
+    void* out;
+    const void* q;
+    const void* qp;
+    const uint8_t* cache;
+    const int32_t* block_tables;
+    const int32_t* seq_lens;
+    const float* kc;
+    const float* vc;
+    float* ws_o;
+    float* ws_ml;
+    int32_t* status;
+    uint32_t* skip_stats;
+    int64_t bt_stride;
+    int64_t num_blocks;
+    float qscale;    // sm_scale * log2(e)
+    float qpscale;   // sm_scale * corr_scale * log2(e)
+    float log2_thresh;
+    int Hq, Hkv, G, ngroups;
+    int sub_per_block;
+    int chunk_pages, max_chunks;
+    int io_dtype;
+};
+
+// ---------------------------------------------------------------------------------
+// Codebook tables in registers: byte k of L[] / H[] is the low / high byte of fp16(c[k]).
+// ---------------------------------------------------------------------------------
+template <int BITS>
+struct Lut {
+    static constexpr int N = (1 << BITS) >= 4 ? (1 << BITS) / 4 : 1;
+    uint32_t L[N];
+    uint32_t H[N];
+    __device__ __forceinline__ void build(const float* __restrict__ c) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = i * 4 + j;
+                const uint32_t h = (k < (1 << BITS)) ? __half_as_ushort(__float2half_rn(__ldg(c + k))) : 0u;
+                lo |= (h & 0xffu) << (8 * j);
+                hi |= (h >> 8) << (8 * j);
+            }
+            L[i] = lo;
+            H[i] = hi;
+        }
+    }
+    // sel: four nibbles (low 16 bits) holding indices of elements e0..e3.
+    // r0 = half2(c[e0], c[e1]), r1 = half2(c[e2], c[e3]).
+    __device__ __forceinline__ void lookup(uint32_t sel, uint32_t& r0, uint32_t& r1) const {
+        uint32_t lo4, hi4;
+        if constexpr (BITS == 2) {
+            lo4 = prmt(L[0], L[0], sel);
+            hi4 = prmt(H[0], H[0], sel);
+        } else if constexpr (BITS == 3) {
+            lo4 = prmt(L[0], L[1], sel);
+            hi4 = prmt(H[0], H[1], sel);
+        } else {
+            // 16 entries: look up in both halves of the table, pick per byte by bit 3 of the nibble.
+            const uint32_t s7 = sel & 0x7777u;
+            const uint32_t m = prmt(sel << 4, sel, 0xD9C8u);  // 0xff where the nibble's top bit is set
+            const uint32_t la = prmt(L[0], L[1], s7), lb = prmt(L[2], L[3], s7);
+            const uint32_t ha = prmt(H[0], H[1], s7), hb = prmt(H[2], H[3], s7);
+            lo4 = (la & ~m) | (lb & m);
+            hi4 = (ha & ~m) | (hb & m);
+        }
+        r0 = prmt(lo4, hi4, 0x5140u);
+        r1 = prmt(lo4, hi4, 0x7362u);
+    }
+};
+
+// Selectors for the 8 groups of 4 elements packed in BITS words (see paged_layout.py).
+template <int BITS>
+__device__ __forceinline__ void selectors(const uint32_t (&w)[BITS], uint32_t (&sel)[8]) {
+    if constexpr (BITS == 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sel[2 * j] = w[j];
+            sel[2 * j + 1] = w[j] >> 16;
+        }
+    } else if constexpr (BITS == 3) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const uint32_t m = w[j] & 0x77777777u;
+            sel[2 * j] = m;
+            sel[2 * j + 1] = m >> 16;
+        }
+        const uint32_t h = ((w[0] >> 3) & 0x11111111u) | ((w[1] >> 2) & 0x22222222u) | ((w[2] >> 1) & 0x44444444u);
+        sel[6] = h;
+        sel[7] = h >> 16;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t a = w[j] & 0x33333333u;
+            const uint32_t b = (w[j] >> 2) & 0x33333333u;
+            sel[4 * j] = a;
+            sel[4 * j + 1] = a >> 16;
+            sel[4 * j + 2] = b;
+            sel[4 * j + 3] = b >> 16;
+        }
+    }
+}
+
+// For a V pair word (token a in the low halves, token b in the high halves) the same
+// masks give a's selector in the low 16 bits and b's in the high 16 bits.
+template <int BITS>
+__device__ __forceinline__ void pair_selectors(const uint32_t (&w)[BITS], uint32_t (&sa)[4], uint32_t (&sb)[4]) {
+    if constexpr (BITS == 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            sa[u] = w[u];
+            sb[u] = w[u] >> 16;
+        }
+    } else if constexpr (BITS == 3) {
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            const uint32_t m = w[u] & 0x77777777u;
+            sa[u] = m;
+            sb[u] = m >> 16;
+        }
+        const uint32_t h = ((w[0] >> 3) & 0x11111111u) | ((w[1] >> 2) & 0x22222222u) | ((w[2] >> 1) & 0x44444444u);
+        sa[3] = h;
+        sb[3] = h >> 16;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t a = w[j] & 0x33333333u;
+            const uint32_t b = (w[j] >> 2) & 0x33333333u;
+            sa[2 * j] = a;
+            sb[2 * j] = a >> 16;
+            sa[2 * j + 1] = b;
+            sb[2 * j + 1] = b >> 16;
+        }
+    }
+}
+
+// Sign word -> half2(+-1, +-1) for pair j (elements at bits j and j + 16).
+__device__ __forceinline__ uint32_t sign_pair(uint32_t sw, int j) {
+    // bit = 1 means +1: fp16 sign bit must be the complement.
+    return (((~sw) << (15 - j)) & 0x80008000u) | 0x3C003C00u;
+}
+
+template <int NW>
+__device__ __forceinline__ void lds_words(const uint8_t* p, uint32_t (&w)[NW]) {
+    if constexpr (NW == 4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else if constexpr (NW == 2) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        w[0] = v.x; w[1] = v.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = *reinterpret_cast<const uint32_t*>(p + 4 * i);
+    }
+}
+
+// Load one query row slice (32 values at q[32*tig ..]) scaled, as 16 half2 registers.
+__device__ __forceinline__ void load_q_frag(const void* q, int64_t row_off, int tig, int io_dtype, float scale,
+                                            bool valid, uint32_t (&f)[16]) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[i] = 0u;
+        return;
+    }
+    const uint16_t* base = static_cast<const uint16_t*>(q) + row_off + tig * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + i);
+        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            if (io_dtype == TQ_DTYPE_F16) {
+                const float2 t = unpack_half2(r[j]);
+                lo = t.x; hi = t.y;
+            } else {
+                lo = __uint_as_float(r[j] << 16);
+                hi = __uint_as_float(r[j] & 0xffff0000u);
+            }
+            f[i * 4 + j] = pack_half2(lo * scale, hi * scale);
+        }
+    }
+}
+
+template <int KB, int VB, bool QJL, bool SPARSE, int NSTAGE>
+__global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const DecodeParams p) {
+    constexpr int NWK = KB + (QJL ? 1 : 0);
+    constexpr int RK = 16 * NWK;
+    constexpr int KN_OFF = 16 * RK;
+    constexpr int KRN_OFF = KN_OFF + 32;
+    constexpr int KPART = KN_OFF + 32 + (QJL ? 32 : 0);
+    constexpr int VN_OFF = KPART + 256 * VB;
+    constexpr int PAGE = KPART + 256 * VB + 32;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                 // [kWarps][2 * NSTAGE]
+    uint8_t* ring = smem + kBarBytes;                                   // [kWarps][NSTAGE][PAGE]
+    float* sm_o = reinterpret_cast<float*>(ring);                       // reused after the page loop
+    __shared__ float sm_m[kWarps][8];
+    __shared__ float sm_l[kWarps][8];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int chunk = blockIdx.x;
+    const int kvh = blockIdx.y / p.ngroups, qg = blockIdx.y % p.ngroups;
+    const int seq = blockIdx.z;
+    const int L = p.seq_lens[seq];
+    const int npages = (L + kPageTokens - 1) / kPageTokens;
+    const int g_in_group = qg * 8 + gid;                // query index inside the GQA group
+    const int nq = min(8, p.G - qg * 8);                // live query heads in this CTA
+    const int head0 = kvh * p.G + qg * 8;
+
+    if (L <= 0) {
+        if (chunk == 0) {  // zeros for empty sequences
+            for (int i = threadIdx.x; i < nq * kHeadDim; i += kThreads) {
+                const int64_t o = (static_cast<int64_t>(seq) * p.Hq + head0 + i / kHeadDim) * kHeadDim + i % kHeadDim;
+                static_cast<uint16_t*>(p.out)[o] = 0;
+            }
+        }
+        return;
+    }
+    const int p0 = chunk * p.chunk_pages;
+    if (p0 >= npages) return;
+    const int p1 = min(p0 + p.chunk_pages, npages);
+    const int n_my = (p0 + warp < p1) ? (p1 - p0 - warp + kWarps - 1) / kWarps : 0;
+
+    uint64_t* mybar = bars + warp * 2 * NSTAGE;        // [0..NSTAGE) K (or whole page), [NSTAGE..) V
+    uint8_t* myring = ring + warp * NSTAGE * PAGE;
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < 2 * NSTAGE; ++s) mbar_init(mybar + s, 1);
+        fence_barrier_init();
+    }
+    __syncwarp();
+
+    // ---- per-warp constants: codebooks and query fragments --------------------------
+    Lut<KB> klut;
+    Lut<VB> vlut;
+    klut.build(p.kc);
+    vlut.build(p.vc);
+    uint32_t qf[16], qpf[QJL ? 16 : 1];
+    {
+        const bool valid = g_in_group < p.G;
+        const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
+        load_q_frag(p.q, row, tig, p.io_dtype, p.qscale, valid, qf);
+        if constexpr (QJL) load_q_frag(p.qp ? p.qp : p.q, row, tig, p.io_dtype, p.qpscale, valid, qpf);
+    }
+
+    // ---- block-table window: lane l holds the entry of this warp's page jbase + l ---
+    const int32_t* bt = p.block_tables + static_cast<int64_t>(seq) * p.bt_stride;
+    int jbase = 0;
+    int32_t btreg = 0;
+    bool bad_block = false;
+    auto load_bt = [&](int jb) {
+        jbase = jb;
+        const int j = jb + lane;
+        int32_t b = 0;
+        if (j < n_my) {
+            b = __ldg(bt + (p0 + warp + kWarps * j) / p.sub_per_block);
+            if (b < 0 || b >= p.num_blocks) {
+                bad_block = true;
+                b = 0;
+            }
+        }
+        btreg = b;
+    };
+    auto page_src = [&](int j) -> const uint8_t* {
+        const int32_t blk = __shfl_sync(0xffffffffu, btreg, j - jbase);
+        const int pg = p0 + warp + kWarps * j;
+        const int sub = pg % p.sub_per_block;
+        return p.cache + ((static_cast<int64_t>(blk) * p.Hkv + kvh) * p.sub_per_block + sub) * PAGE;
+    };
+    // Dense mode: one copy of the whole page.  Sparse mode: K part now, V part on demand.
+    auto issue_k = [&](int j) {
+        const uint8_t* src = page_src(j);
+        const int s = j % NSTAGE;
+        if (lane == 0) {
+            constexpr uint32_t bytes = SPARSE ? KPART : PAGE;
+            mbar_expect_tx(mybar + s, bytes);
+            bulk_g2s(myring + s * PAGE, src, bytes, mybar + s);
+        }
+    };
+    auto issue_v = [&](int j) {
+        const uint8_t* src = page_src(j);
+        const int s = j % NSTAGE;
+        if (lane == 0) {
+            mbar_expect_tx(mybar + NSTAGE + s, PAGE - KPART);
+            bulk_g2s(myring + s * PAGE + KPART, src + KPART, PAGE - KPART, mybar + NSTAGE + s);
+        }
+    };
+
+    if (n_my > 0) load_bt(0);
+#pragma unroll
+    for (int j = 0; j < NSTAGE; ++j)
+        if (j < n_my) issue_k(j);
+
+    // ---- online-softmax state ---------------------------------------------------------
+    float m0 = -INFINITY, m1 = -INFINITY;   // running max for queries 2*tig, 2*tig+1 (log2 domain)
+    float l0 = 0.f, l1 = 0.f;               // this lane's share of the denominators
+    float oacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) oacc[i][r] = 0.f;
+    bool timed_out = false;
+    uint32_t v_seen = 0, v_skipped = 0;
+    uint32_t v_parity = 0;                  // bit s: phase of the V barrier of stage s (sparse mode)
+    int j_stop = n_my;
+
+    for (int j = 0; j < n_my; ++j) {
+        const int s = j % NSTAGE;
+        const uint32_t parity = (j / NSTAGE) & 1;
+        const uint8_t* pg = myring + s * PAGE;
+        if (!mbar_wait_bounded(mybar + s, parity)) {
+            timed_out = true;
+            j_stop = j;
+            break;
+        }
+        const int valid_tokens = min(kPageTokens, L - (p0 + warp + kWarps * j) * kPageTokens);
+
+        // ---- K: dequantise two token rows (gid, gid + 8) and score them against 8 queries
+        uint32_t wa[NWK], wb[NWK];
+        lds_words<NWK>(pg + lane * (NWK * 4), wa);
+        lds_words<NWK>(pg + (lane + 32) * (NWK * 4), wb);
+        uint32_t sela[8], selb[8];
+        {
+            uint32_t ia[KB], ib[KB];
+#pragma unroll
+            for (int i = 0; i < KB; ++i) { ia[i] = wa[i]; ib[i] = wb[i]; }
+            selectors<KB>(ia, sela);
+            selectors<KB>(ib, selb);
+        }
+        float sm[4] = {0.f, 0.f, 0.f, 0.f};
+        float sq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t a0, a1, b0, b1;
+            klut.lookup(sela[c], a0, a1);
+            klut.lookup(selb[c], b0, b1);
+            mma_f16_16816(sm, a0, b0, a1, b1, qf[2 * c], qf[2 * c + 1]);
+            if constexpr (QJL) {
+                mma_f16_16816(sq, sign_pair(wa[KB], 2 * c), sign_pair(wb[KB], 2 * c), sign_pair(wa[KB], 2 * c + 1),
+                              sign_pair(wb[KB], 2 * c + 1), qpf[2 * c], qpf[2 * c + 1]);
+            }
+        }
+        const float2 kn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KN_OFF + gid * 4));
+        float s0 = sm[0] * kn.x, s1 = sm[1] * kn.x, s2 = sm[2] * kn.y, s3 = sm[3] * kn.y;
+        if constexpr (QJL) {
+            const float2 krn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KRN_OFF + gid * 4));
+            s0 = fmaf(sq[0], krn.x, s0);
+            s1 = fmaf(sq[1], krn.x, s1);
+            s2 = fmaf(sq[2], krn.y, s2);
+            s3 = fmaf(sq[3], krn.y, s3);
+        }
+        const bool va = gid < valid_tokens, vb = gid + 8 < valid_tokens;
+        if (!va) { s0 = -INFINITY; s1 = -INFINITY; }
+        if (!vb) { s2 = -INFINITY; s3 = -INFINITY; }
+
+        // ---- online softmax over the 16 tokens (rows live across the 8 gid lanes)
+        float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const bool grew = (mn0 > m0) || (mn1 > m1);
+        float p0v = ex2(s0 - mn0), p1v = ex2(s1 - mn1), p2v = ex2(s2 - mn0), p3v = ex2(s3 - mn1);
+        if (__any_sync(0xffffffffu, grew)) {
+            const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
+            l0 *= al0;
+            l1 *= al1;
+            // accumulator rows belong to query gid: fetch its factor from the lane that scored it
+            const float t0 = __shfl_sync(0xffffffffu, al0, gid >> 1);
+            const float t1 = __shfl_sync(0xffffffffu, al1, gid >> 1);
+            const float ag = (gid & 1) ? t1 : t0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) oacc[i][r] *= ag;
+            m0 = mn0;
+            m1 = mn1;
+        }
+        l0 += p0v + p2v;
+        l1 += p1v + p3v;
+
+        // ---- Sparse-V: skip the page when no weight of the group exceeds the threshold
+        bool do_v = true;
+        if constexpr (SPARSE) {
+            // p = 2^(s - m) in the log2 domain; compare exponents to avoid a second exp.
+            const float e = fmaxf(fmaxf(s0 - mn0, s1 - mn1), fmaxf(s2 - mn0, s3 - mn1));
+            do_v = __any_sync(0xffffffffu, e > p.log2_thresh);
+            ++v_seen;
+            if (!do_v) ++v_skipped;
+        }
+        if (do_v) {
+            if constexpr (SPARSE) {
+                issue_v(j);
+                const bool ok = mbar_wait_bounded(mybar + NSTAGE + s, (v_parity >> s) & 1u);
+                v_parity ^= 1u << s;
+                if (!ok) {
+                    timed_out = true;
+                    j_stop = j;
+                    break;
+                }
+            }
+            const float2 vn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + VN_OFF + gid * 4));
+            const uint32_t pr0 = pack_half2(va ? p0v * vn.x : 0.f, va ? p1v * vn.x : 0.f);
+            const uint32_t pr1 = pack_half2(vb ? p2v * vn.y : 0.f, vb ? p3v * vn.y : 0.f);
+            const uint32_t t[2] = {movmatrix_trans(pr0), movmatrix_trans(pr1)};
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {
+                const uint32_t pa0 = t[o] & 0xffffu, pa1 = t[o] << 16, pa2 = t[o] >> 16, pa3 = t[o] & 0xffff0000u;
+                uint32_t pw[VB];
+#pragma unroll
+                for (int i = 0; i < VB; ++i)
+                    pw[i] = *reinterpret_cast<const uint32_t*>(pg + KPART + ((i * 8 + (4 * o + tig)) * 8 + gid) * 4);
+                uint32_t sa[4], sb[4];
+                pair_selectors<VB>(pw, sa, sb);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t a0, a1, b0, b1;
+                    vlut.lookup(sa[u], a0, a1);
+                    vlut.lookup(sb[u], b0, b1);
+                    mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
+                    mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
+                }
+            }
+        }
+        __syncwarp();
+        if (j + NSTAGE < n_my) {
+            // slide the window by 16 so that entries j .. j + NSTAGE stay available
+            if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
+            issue_k(j + NSTAGE);
+        }
+    }
+    if (timed_out) {
+        // Give copies that were already issued a bounded chance to land before the ring is reused.
+        for (int j = j_stop + 1; j < min(n_my, j_stop + NSTAGE); ++j)
+            (void)mbar_wait_bounded(mybar + j % NSTAGE, (j / NSTAGE) & 1);
+    }
+
+    if (p.status) {
+        int bits = 0;
+        if (__any_sync(0xffffffffu, bad_block)) bits |= TQ_STATUS_BAD_BLOCK;
+        if (__any_sync(0xffffffffu, timed_out)) bits |= TQ_STATUS_TIMEOUT;
+        if (bits && lane == 0) atomicOr(p.status, bits);
+    }
+    if constexpr (SPARSE) {
+        if (p.skip_stats && lane == 0) {
+            atomicAdd(p.skip_stats, v_seen);
+            atomicAdd(p.skip_stats + 1, v_skipped);
+        }
+    }
+
+    // ---- merge the 4 warps --------------------------------------------------------------
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
+    __syncthreads();  // every warp is done with its ring; it becomes the merge buffer
+    if (gid == 0) {
+        sm_m[warp][2 * tig] = m0;
+        sm_m[warp][2 * tig + 1] = m1;
+        sm_l[warp][2 * tig] = l0;
+        sm_l[warp][2 * tig + 1] = l1;
+    }
+    {
+        float* row = sm_o + (warp * 8 + gid) * kOPad;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int dim = 16 * (2 * tig + (r & 1)) + 2 * nt + (r >> 1);
+                row[dim + (dim >> 5)] = oacc[nt][r];
+            }
+    }
+    __syncthreads();
+    const int dim = threadIdx.x;
+    const int col = dim + (dim >> 5);
+    const int nchunks = (npages + p.chunk_pages - 1) / p.chunk_pages;
+    for (int g = 0; g < nq; ++g) {
+        float M = sm_m[0][g];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) M = fmaxf(M, sm_m[w][g]);
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float sc = ex2(sm_m[w][g] - M);
+            o = fmaf(sc, sm_o[(w * 8 + g) * kOPad + col], o);
+            l = fmaf(sc, sm_l[w][g], l);
+        }
+        if (nchunks == 1) {
+            const float r = o / l;
+            const int64_t off = (static_cast<int64_t>(seq) * p.Hq + head0 + g) * kHeadDim + dim;
+            if (p.io_dtype == TQ_DTYPE_F16)
+                static_cast<__half*>(p.out)[off] = __float2half_rn(r);
+            else
+                static_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(r);
+        } else {
+            const int64_t slot = ((static_cast<int64_t>(seq) * p.Hkv * p.ngroups + blockIdx.y) * p.max_chunks + chunk) * 8 + g;
+            p.ws_o[slot * kHeadDim + dim] = o;
+            if (dim == 0) {
+                p.ws_ml[slot * 2] = M;
+                p.ws_ml[slot * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const DecodeParams p) {
+    const int head = blockIdx.x, seq = blockIdx.y, dim = threadIdx.x;
+    const int L = p.seq_lens[seq];
+    const int npages = (L + kPageTokens - 1) / kPageTokens;
+    const int nchunks = (npages + p.chunk_pages - 1) / p.chunk_pages;
+    if (nchunks <= 1) return;  // written by the partial kernel
+    const int kvh = head / p.G, gi = head % p.G;
+    const int by = kvh * p.ngroups + gi / 8, g = gi % 8;
+    const int64_t base = (static_cast<int64_t>(seq) * p.Hkv * p.ngroups + by) * p.max_chunks;
+    float M = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) M = fmaxf(M, p.ws_ml[((base + c) * 8 + g) * 2]);
+    float o = 0.f, l = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+        const int64_t slot = (base + c) * 8 + g;
+        const float sc = ex2(p.ws_ml[slot * 2] - M);
+        o = fmaf(sc, p.ws_o[slot * kHeadDim + dim], o);
+        l = fmaf(sc, p.ws_ml[slot * 2 + 1], l);
+    }
+    const float r = o / l;
+    const int64_t off = (static_cast<int64_t>(seq) * p.Hq + head) * kHeadDim + dim;
+    if (p.io_dtype == TQ_DTYPE_F16)
+        static_cast<__half*>(p.out)[off] = __float2half_rn(r);
+    else
+        static_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16_rn(r);
+}
+
+template <int KB, int VB, bool QJL, bool SPARSE>
+int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr int PAGE = page_bytes(KB, VB, QJL ? 1 : 0);
+    constexpr size_t smem = kBarBytes + static_cast<size_t>(kWarps) * kStages * PAGE;
+    static_assert(static_cast<size_t>(kWarps) * kStages * PAGE >= sizeof(float) * kWarps * 8 * kOPad,
+                  "ring must hold the merge buffer");
+    auto kern = decode_partial_kernel<KB, VB, QJL, SPARSE, kStages>;
+    // The opt-in shared-memory size is a per-device function attribute; set once per device.
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TQ_ERR_LAUNCH;
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return TQ_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    kern<<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+template <int KB, int VB>
+int dispatch_flags(const DecodeParams& p, bool qjl, bool sparse, dim3 grid, cudaStream_t stream) {
+    if (qjl) return sparse ? launch_partial<KB, VB, true, true>(p, grid, stream) : launch_partial<KB, VB, true, false>(p, grid, stream);
+    return sparse ? launch_partial<KB, VB, false, true>(p, grid, stream) : launch_partial<KB, VB, false, false>(p, grid, stream);
+}
+
+template <int KB>
+int dispatch_v(const DecodeParams& p, int vb, bool qjl, bool sparse, dim3 grid, cudaStream_t stream) {
+    switch (vb) {
+        case 2: return dispatch_flags<KB, 2>(p, qjl, sparse, grid, stream);
+        case 3: return dispatch_flags<KB, 3>(p, qjl, sparse, grid, stream);
+        case 4: return dispatch_flags<KB, 4>(p, qjl, sparse, grid, stream);
+    }
+    return TQ_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int num_q_heads, int max_pages_per_seq) {
+    if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    // Aim for ~8 CTAs per resident slot (148 SMs x 4 CTAs) so the tail of the last wave is small,
+    // but keep at least 8 pages per warp so the per-CTA prologue and merge stay amortised.
+    const int G = num_q_heads / num_kv_heads;
+    const int ngroups = (G + 7) / 8;
+    const long long pairs = 1LL * num_seqs * num_kv_heads * ngroups;
+    const long long target_ctas = 148LL * 4 * 8;
+    long long chunks = (target_ctas + pairs - 1) / pairs;
+    if (chunks < 1) chunks = 1;
+    long long cp = (max_pages_per_seq + chunks - 1) / chunks;
+    if (cp < 32) cp = 32;
+    if (cp > max_pages_per_seq) cp = max_pages_per_seq;
+    return static_cast<int>(cp);
+}
+
+extern "C" int64_t tq_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq,
+                                             int chunk_pages) {
+    if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    if (chunk_pages <= 0) chunk_pages = tq_decode_auto_chunk_pages(num_seqs, num_kv_heads, num_q_heads, max_pages_per_seq);
+    const int G = num_q_heads / num_kv_heads;
+    const int ngroups = (G + 7) / 8;
+    const int64_t max_chunks = (max_pages_per_seq + chunk_pages - 1) / chunk_pages;
+    const int64_t slots = static_cast<int64_t>(num_seqs) * num_kv_heads * ngroups * max_chunks * 8;
+    return slots * (kHeadDim + 2) * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj, int io_dtype, const void* cache,
+                               int64_t num_blocks, int block_size, const int32_t* block_tables, int64_t bt_stride,
+                               const int32_t* seq_lens, const float* k_centroids, const float* v_centroids,
+                               float sm_scale, float corr_scale, float sparse_thresh, void* workspace,
+                               int64_t workspace_bytes, int32_t* status, uint32_t* skip_stats, int num_seqs,
+                               int num_q_heads, int num_kv_heads, int max_pages_per_seq, int k_bits, int v_bits,
+                               int use_qjl, int chunk_pages, tq_stream_t stream) {
+    if (num_seqs == 0) return TQ_OK;
+    if (!out || !q_rot || !cache || !block_tables || !seq_lens || !k_centroids || !v_centroids) return TQ_ERR_ARG;
+    if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0 || num_blocks <= 0) return TQ_ERR_ARG;
+    if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
+    if (io_dtype != TQ_DTYPE_F16 && io_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
+    if (block_size <= 0 || block_size % kPageTokens) return TQ_ERR_UNSUPPORTED;
+    if (k_bits < 2 || k_bits > 4 || v_bits < 2 || v_bits > 4) return TQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(q_rot) | reinterpret_cast<uintptr_t>(out) |
+         reinterpret_cast<uintptr_t>(q_proj)) & 15)
+        return TQ_ERR_ARG;
+    if (chunk_pages <= 0) chunk_pages = tq_decode_auto_chunk_pages(num_seqs, num_kv_heads, num_q_heads, max_pages_per_seq);
+    const int64_t need = tq_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, max_pages_per_seq, chunk_pages);
+    const int max_chunks = (max_pages_per_seq + chunk_pages - 1) / chunk_pages;
+    if (max_chunks > 1 && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)))
+        return TQ_ERR_WORKSPACE;
+    if (num_seqs > 65535 || max_chunks > 65535) return TQ_ERR_UNSUPPORTED;
+
+    DecodeParams p;
+    p.out = out;
+    p.q = q_rot;
+    p.qp = q_proj;
+    p.cache = static_cast<const uint8_t*>(cache);
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.kc = k_centroids;
+    p.vc = v_centroids;
+    p.G = num_q_heads / num_kv_heads;
+    p.ngroups = (p.G + 7) / 8;
+    const int64_t slots = static_cast<int64_t>(num_seqs) * num_kv_heads * p.ngroups * max_chunks * 8;
+    p.ws_o = static_cast<float*>(workspace);
+    p.ws_ml = p.ws_o ? p.ws_o + slots * kHeadDim : nullptr;
+    p.status = status;
+    p.skip_stats = skip_stats;
+    p.bt_stride = bt_stride;
+    p.num_blocks = num_blocks;
+    p.qscale = sm_scale * kLog2e;
+    p.qpscale = sm_scale * corr_scale * kLog2e;
+    p.log2_thresh = sparse_thresh > 0.f ? log2f(sparse_thresh) : -INFINITY;
+    p.Hq = num_q_heads;
+    p.Hkv = num_kv_heads;
+    p.sub_per_block = block_size / kPageTokens;
+    p.chunk_pages = chunk_pages;
+    p.max_chunks = max_chunks;
+    p.io_dtype = io_dtype;
+
+    const dim3 grid(max_chunks, num_kv_heads * p.ngroups, num_seqs);
+    const bool qjl = use_qjl != 0, sparse = sparse_thresh > 0.f;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int rc;
+    switch (k_bits) {
+        case 2: rc = dispatch_v<2>(p, v_bits, qjl, sparse, grid, st); break;
+        case 3: rc = dispatch_v<3>(p, v_bits, qjl, sparse, grid, st); break;
+        case 4: rc = dispatch_v<4>(p, v_bits, qjl, sparse, grid, st); break;
+        default: return TQ_ERR_UNSUPPORTED;
+    }
+    if (rc != TQ_OK) return rc;
+    if (max_chunks > 1) {
+        decode_merge_kernel<<<dim3(num_q_heads, num_seqs), kHeadDim, 0, st>>>(p);
+        if (cudaGetLastError() != cudaSuccess) return TQ_ERR_LAUNCH;
+    }
+    return TQ_OK;
+}
