@@ -274,8 +274,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
     {
         const bool valid = g_in_group < p.G;
         const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
-        load_q_frag(p.q, row, tig, p.io_dtype, p.qscale, valid, qf);
-        if constexpr (QJL) load_q_frag(p.qp ? p.qp : p.q, row, tig, p.io_dtype, p.qpscale, valid, qpf);
+        load_q_frag(p.q, row, tig, p.io_dtype, 1.f, valid, qf);
+        if constexpr (QJL) load_q_frag(p.qp ? p.qp : p.q, row, tig, p.io_dtype, 1.f, valid, qpf);
     }
 
     // ---- block-table window: lane l holds the entry of this warp's page jbase + l ---
@@ -375,10 +375,16 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
                               sign_pair(wb[KB], 2 * c + 1), qpf[2 * c], qpf[2 * c + 1]);
             }
         }
-        const float2 kn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KN_OFF + gid * 4));
+        // The softmax scale (and log2 e) is applied to the fp32 norms, not to the fp16 query, so the
+        // query fragments are the caller's fp16 values exactly.
+        float2 kn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KN_OFF + gid * 4));
+        kn.x *= p.qscale;
+        kn.y *= p.qscale;
         float s0 = sm[0] * kn.x, s1 = sm[1] * kn.x, s2 = sm[2] * kn.y, s3 = sm[3] * kn.y;
         if constexpr (QJL) {
-            const float2 krn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KRN_OFF + gid * 4));
+            float2 krn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KRN_OFF + gid * 4));
+            krn.x *= p.qpscale;
+            krn.y *= p.qpscale;
             s0 = fmaf(sq[0], krn.x, s0);
             s1 = fmaf(sq[1], krn.x, s1);
             s2 = fmaf(sq[2], krn.y, s2);

@@ -103,17 +103,15 @@ def check_is_wht(matrix: torch.Tensor, d: int) -> None:
     """Raise unless `matrix` is the normalised Sylvester WHT matrix the fast transform implements."""
     if d != 128 or tuple(matrix.shape) != (128, 128):
         raise ValueError("only head_dim 128 is supported")
-    key = (matrix.data_ptr(), matrix._version, matrix.device)
-    if key in _wht_ok:
+    # The verdict is remembered on the tensor object itself (and dropped if it is written to),
+    # so a matrix is compared once, not on every call.
+    if getattr(matrix, "_tq_is_wht_version", None) == matrix._version:
         return
     from turboquant.core.rotation import make_wht_matrix
     if not torch.allclose(matrix.detach().float().cpu(), make_wht_matrix(128), atol=1e-6, rtol=0):
         raise ValueError("rotation_matrix must be make_wht_matrix(128): the kernels apply that rotation as a "
                          "fast Walsh-Hadamard transform and cannot apply an arbitrary matrix")
-    _wht_ok.add(key)
-
-
-_wht_ok: set = set()
+    matrix._tq_is_wht_version = matrix._version
 
 # ---- per-device scratch: status word, split-K workspaces --------------------------------------
 _status: dict = {}
