@@ -180,7 +180,7 @@ def test_compress_paged_prerotated_strided_and_bad_slots():
     key, val = qkv[:, Hkv:2 * Hkv], qkv[:, 2 * Hkv:]
     slots = torch.arange(T, dtype=torch.int64)
     slots[3] = -1                                                       # padding slot -> clamped to 0 (like the reference)
-    slots[0] = 5                                                        # so slot 0 is written by token 3 only
+    slots[0] = 45                                                       # so slot 0 is written by token 3 only
     slots[7] = nb * bs + 3                                              # beyond the cache -> skipped and flagged
     cache = allocate_cache(nb, bs, Hkv, fmt, DEV)
     compress_and_scatter(key, val, cache, slots.to(DEV), books, bs, prerotated=True)
@@ -190,7 +190,7 @@ def test_compress_paged_prerotated_strided_and_bad_slots():
                                books.kb.cpu().numpy(), 3, True, None)
     want = ok["indices"].reshape(T, Hkv, 128)
     assert np.array_equal(f["k_idx"][0, 0].numpy(), want[3])            # token 3 landed in slot 0
-    assert np.array_equal(f["k_idx"][0, 5].numpy(), want[0])
+    assert np.array_equal(f["k_idx"][2, 13].numpy(), want[0])           # slot 45 = block 2, offset 13
     assert np.array_equal(f["k_idx"][0, 9].numpy(), want[9])
     assert (f["k_idx"][0, 7] == 0).all()                                # token 7 was skipped; slot 7 untouched (zeros)
     with pytest.raises(ValueError):

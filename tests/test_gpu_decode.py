@@ -127,7 +127,7 @@ def test_decode_peaked_logits_and_sparse_v():
     f = random_fields(fmt, 130, 16, 1, 3)
     cache = paged_layout.pack_cache(f, 16, 3, 3, True).to(DEV)
     bt = torch.arange(125, dtype=torch.int32).reshape(1, 125).to(DEV)
-    q = (torch.randn(1, 8, 128, generator=torch.Generator().manual_seed(1)) * 6).half().to(DEV)
+    q = (torch.randn(1, 8, 128, generator=torch.Generator().manual_seed(1)) * 40).half().to(DEV)
     stats = torch.zeros(2, dtype=torch.int32, device=DEV)
     paged_decode_attention(q, cache, bt, torch.tensor([2000], dtype=torch.int32, device=DEV), books, 16,
                            sparse_thresh=1e-6, skip_stats=stats)
