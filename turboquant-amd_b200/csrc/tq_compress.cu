@@ -137,10 +137,7 @@ __device__ __forceinline__ void store_k_paged(uint8_t* page, int t, int lane, co
         w[j] = __reduce_or_sync(gmask, v);
     }
     if constexpr (QJL) {
-        uint32_t v = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) v |= ((q.sign4 >> e) & 1u) << ((e & 1) * 16 + 2 * c + (e >> 1));
-        w[BITS] = __reduce_or_sync(gmask, v);
+        w[BITS] = __reduce_or_sync(gmask, q.sign4 << (4 * c));   // bit l = sign of dim 32 * quarter + l
     }
     if (c == 0) {
         uint8_t* dst = page + t * RK + quarter * (RK / 4);

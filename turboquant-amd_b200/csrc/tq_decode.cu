@@ -46,10 +46,11 @@ struct DecodeParams {
     int64_t bt_stride;
     int64_t num_blocks;
     float qscale;    // sm_scale * log2(e)
-    float qpscale;   // sm_scale * corr_scale * log2(e)
+    float qpscale;   // sm_scale * corr_scale * log2(e) * 16
     float log2_thresh;
     int Hq, Hkv, G, ngroups;
-    int sub_per_block;
+    int sub_shift;           // log2(block_size / 16)
+    int64_t block_stride;    // bytes between consecutive blocks of the cache
     int chunk_pages, max_chunks;
     int io_dtype;
 };
@@ -166,10 +167,53 @@ __device__ __forceinline__ void pair_selectors(const uint32_t (&w)[BITS], uint32
     }
 }
 
-// Sign word -> half2(+-1, +-1) for pair j (elements at bits j and j + 16).
-__device__ __forceinline__ uint32_t sign_pair(uint32_t sw, int j) {
-    // bit = 1 means +1: fp16 sign bit must be the complement.
-    return (((~sw) << (15 - j)) & 0x80008000u) | 0x3C003C00u;
+// QJL sign term on fp16 tensor cores with one logic op per pair of signs.
+//
+// The sign word holds bit l = 1 when the residual of local dim l is >= 0.  A register of the
+// A fragment is a pair of dims (j, j + 16), i.e. bits j and j + 16.  After x = sw << k the pair
+// whose bits landed on 15/31 is turned into +-1 by one and-or; the pairs on bits 14/30, 13/29
+// and 12/28 are used as they are: a lone exponent bit of an fp16 number is the value 2, 2^-7 or
+// 2^-11.  Those three forms give (value) * [sign >= 0] instead of +-1; since
+// 2 * [s >= 0] = sigma + 1, the query operand of those slots is pre-scaled (1, 2^8, 2^12) and
+// the constant sum of the query over those dims is subtracted once (accumulator start value).
+// Form 0 yields -sigma, so its query operand is negated.  All query operands carry 1/16 to keep
+// 2^12 * q inside fp16; the factor 16 is folded into the fp32 scale of the residual norm.
+__device__ __forceinline__ void load_qp_frag_signed(const void* q, int64_t row_off, int tig, int io_dtype, bool valid,
+                                                    uint32_t (&f)[16], float& correction) {
+    correction = 0.f;
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[i] = 0u;
+        return;
+    }
+    const uint16_t* base = static_cast<const uint16_t*>(q) + row_off + tig * 32;
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + i);
+        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (io_dtype == TQ_DTYPE_F16) {
+                const float2 t = unpack_half2(r[j]);
+                x[8 * i + 2 * j] = t.x;
+                x[8 * i + 2 * j + 1] = t.y;
+            } else {
+                x[8 * i + 2 * j] = __uint_as_float(r[j] << 16);
+                x[8 * i + 2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+            }
+        }
+    }
+    const float coef[4] = {-1.f / 16.f, 1.f / 16.f, 16.f, 256.f};   // form 0..3, times the common 1/16
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+            const int form = 2 * (m & 1) + sl, k = 4 * (m >> 1), j = 15 - form - k;
+            f[2 * m + sl] = pack_half2(coef[form] * x[j], coef[form] * x[j + 16]);
+            if (form) correction += (x[j] + x[j + 16]) * (1.f / 16.f);
+        }
+    }
 }
 
 template <int NW>
@@ -271,11 +315,19 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
     klut.build(p.kc);
     vlut.build(p.vc);
     uint32_t qf[16], qpf[QJL ? 16 : 1];
+    float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
     {
         const bool valid = g_in_group < p.G;
         const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
         load_q_frag(p.q, row, tig, p.io_dtype, 1.f, valid, qf);
-        if constexpr (QJL) load_q_frag(p.qp ? p.qp : p.q, row, tig, p.io_dtype, 1.f, valid, qpf);
+        if constexpr (QJL) {
+            float corr;
+            load_qp_frag_signed(p.qp ? p.qp : p.q, row, tig, p.io_dtype, valid, qpf, corr);
+            corr += __shfl_xor_sync(0xffffffffu, corr, 1);
+            corr += __shfl_xor_sync(0xffffffffu, corr, 2);      // total over the 128 dims of query gid
+            sq_init0 = -__shfl_sync(0xffffffffu, corr, 8 * tig);       // query 2 * tig lives on lanes 8 * tig ..
+            sq_init1 = -__shfl_sync(0xffffffffu, corr, 8 * tig + 4);   // query 2 * tig + 1
+        }
     }
 
     // ---- block-table window: lane l holds the entry of this warp's page jbase + l ---
@@ -288,7 +340,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
         const int j = jb + lane;
         int32_t b = 0;
         if (j < n_my) {
-            b = __ldg(bt + (p0 + warp + kWarps * j) / p.sub_per_block);
+            b = __ldg(bt + ((p0 + warp + kWarps * j) >> p.sub_shift));
             if (b < 0 || b >= p.num_blocks) {
                 bad_block = true;
                 b = 0;
@@ -296,11 +348,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
         }
         btreg = b;
     };
+    const uint8_t* head_base = p.cache + (static_cast<int64_t>(kvh) << p.sub_shift) * PAGE;
     auto page_src = [&](int j) -> const uint8_t* {
         const int32_t blk = __shfl_sync(0xffffffffu, btreg, j - jbase);
         const int pg = p0 + warp + kWarps * j;
-        const int sub = pg % p.sub_per_block;
-        return p.cache + ((static_cast<int64_t>(blk) * p.Hkv + kvh) * p.sub_per_block + sub) * PAGE;
+        const int sub = pg & ((1 << p.sub_shift) - 1);
+        return head_base + static_cast<int64_t>(blk) * p.block_stride + sub * PAGE;
     };
     // Dense mode: one copy of the whole page.  Sparse mode: K part now, V part on demand.
     auto issue_k = [&](int j) {
@@ -370,9 +423,18 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
             klut.lookup(sela[c], a0, a1);
             klut.lookup(selb[c], b0, b1);
             mma_f16_16816(sm, a0, b0, a1, b1, qf[2 * c], qf[2 * c + 1]);
-            if constexpr (QJL) {
-                mma_f16_16816(sq, sign_pair(wa[KB], 2 * c), sign_pair(wb[KB], 2 * c), sign_pair(wa[KB], 2 * c + 1),
-                              sign_pair(wb[KB], 2 * c + 1), qpf[2 * c], qpf[2 * c + 1]);
+        }
+        float sq2[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (QJL) {
+            sq[0] = sq[2] = sq_init0;
+            sq[1] = sq[3] = sq_init1;
+#pragma unroll
+            for (int ki = 0; ki < 4; ++ki) {
+                const uint32_t xa = wa[KB] << (4 * ki), xb = wb[KB] << (4 * ki);
+                mma_f16_16816(sq, (xa & 0x80008000u) | 0x3C003C00u, (xb & 0x80008000u) | 0x3C003C00u,
+                              xa & 0x40004000u, xb & 0x40004000u, qpf[4 * ki], qpf[4 * ki + 1]);
+                mma_f16_16816(sq2, xa & 0x20002000u, xb & 0x20002000u, xa & 0x10001000u, xb & 0x10001000u,
+                              qpf[4 * ki + 2], qpf[4 * ki + 3]);
             }
         }
         // The softmax scale (and log2 e) is applied to the fp32 norms, not to the fp16 query, so the
@@ -385,14 +447,19 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
             float2 krn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KRN_OFF + gid * 4));
             krn.x *= p.qpscale;
             krn.y *= p.qpscale;
-            s0 = fmaf(sq[0], krn.x, s0);
-            s1 = fmaf(sq[1], krn.x, s1);
-            s2 = fmaf(sq[2], krn.y, s2);
-            s3 = fmaf(sq[3], krn.y, s3);
+            s0 = fmaf(sq[0] + sq2[0], krn.x, s0);
+            s1 = fmaf(sq[1] + sq2[1], krn.x, s1);
+            s2 = fmaf(sq[2] + sq2[2], krn.y, s2);
+            s3 = fmaf(sq[3] + sq2[3], krn.y, s3);
         }
-        const bool va = gid < valid_tokens, vb = gid + 8 < valid_tokens;
-        if (!va) { s0 = -INFINITY; s1 = -INFINITY; }
-        if (!vb) { s2 = -INFINITY; s3 = -INFINITY; }
+        // only the last page of a sequence can be partly filled
+        bool va = true, vb = true;
+        if (valid_tokens < kPageTokens) {
+            va = gid < valid_tokens;
+            vb = gid + 8 < valid_tokens;
+            if (!va) { s0 = -INFINITY; s1 = -INFINITY; }
+            if (!vb) { s2 = -INFINITY; s3 = -INFINITY; }
+        }
 
         // ---- online softmax over the 16 tokens (rows live across the 8 gid lanes)
         float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
@@ -616,16 +683,17 @@ using namespace tq;
 
 extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int num_q_heads, int max_pages_per_seq) {
     if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
-    // Aim for ~8 CTAs per resident slot (148 SMs x 4 CTAs) so the tail of the last wave is small,
-    // but keep at least 8 pages per warp so the per-CTA prologue and merge stay amortised.
+    // About 3 CTAs per resident slot (148 SMs x 4 CTAs) keeps the tail of the last wave small; at
+    // least 64 pages per CTA (16 per warp) keeps the per-CTA prologue and merge amortised.  Measured on
+    // batch 64 x 8192 tokens x 8 KV heads: 128..256 pages per chunk is the flat optimum.
     const int G = num_q_heads / num_kv_heads;
     const int ngroups = (G + 7) / 8;
     const long long pairs = 1LL * num_seqs * num_kv_heads * ngroups;
-    const long long target_ctas = 148LL * 4 * 8;
+    const long long target_ctas = 148LL * 4 * 3;
     long long chunks = (target_ctas + pairs - 1) / pairs;
     if (chunks < 1) chunks = 1;
     long long cp = (max_pages_per_seq + chunks - 1) / chunks;
-    if (cp < 32) cp = 32;
+    if (cp < 64) cp = 64;
     if (cp > max_pages_per_seq) cp = max_pages_per_seq;
     return static_cast<int>(cp);
 }
@@ -653,7 +721,7 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0 || num_blocks <= 0) return TQ_ERR_ARG;
     if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
     if (io_dtype != TQ_DTYPE_F16 && io_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
-    if (block_size <= 0 || block_size % kPageTokens) return TQ_ERR_UNSUPPORTED;
+    if (block_size < kPageTokens || (block_size & (block_size - 1))) return TQ_ERR_UNSUPPORTED;  // 16, 32, 64, ...
     if (k_bits < 2 || k_bits > 4 || v_bits < 2 || v_bits > 4) return TQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(q_rot) | reinterpret_cast<uintptr_t>(out) |
          reinterpret_cast<uintptr_t>(q_proj)) & 15)
@@ -684,11 +752,14 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     p.bt_stride = bt_stride;
     p.num_blocks = num_blocks;
     p.qscale = sm_scale * kLog2e;
-    p.qpscale = sm_scale * corr_scale * kLog2e;
+    p.qpscale = sm_scale * corr_scale * kLog2e * 16.f;   // the sign-term query operands carry 1/16
     p.log2_thresh = sparse_thresh > 0.f ? log2f(sparse_thresh) : -INFINITY;
     p.Hq = num_q_heads;
     p.Hkv = num_kv_heads;
-    p.sub_per_block = block_size / kPageTokens;
+    p.sub_shift = 0;
+    while ((kPageTokens << p.sub_shift) < block_size) ++p.sub_shift;
+    p.block_stride = static_cast<int64_t>(num_kv_heads) * (block_size / kPageTokens) *
+                     page_bytes(k_bits, v_bits, use_qjl ? 1 : 0);
     p.chunk_pages = chunk_pages;
     p.max_chunks = max_chunks;
     p.io_dtype = io_dtype;

@@ -22,7 +22,7 @@ K part
            c >= 6: bit b of the index sits in word b at (c - 6) * 16 + 4 e + 3
                    (the spare top bit of each nibble)
     2-bit: word c >> 2, bits (c & 1) * 16 + 4 e + ((c >> 1) & 1) * 2 + [0..1]
-    sign : sign word, bit (e & 1) * 16 + 2 c + (e >> 1); 1 means residual >= 0
+    sign : sign word, bit 4 c + e (= d & 31); 1 means residual >= 0
   then fp16 norms at 16 * RK in the order slot(t) = (t & 7) * 2 + (t >> 3),
   and, with QJL, fp16 residual norms in the same order.
 
@@ -121,7 +121,7 @@ def _k_bit_position(bits: int, rk: int, t: int, d: int, b: int) -> int:
 def _k_sign_position(bits: int, rk: int, t: int, d: int) -> int:
     q, c, e = d >> 5, (d >> 2) & 7, d & 3
     base = (t * rk + q * (rk // 4)) * 8 + bits * 32
-    return base + (e & 1) * 16 + 2 * c + (e >> 1)
+    return base + 4 * c + e
 
 
 def _v_bit_position(bits: int, voff: int, t: int, d: int, b: int) -> int:
