@@ -119,6 +119,35 @@ int tq_decode_paged(void* out, const void* q_rot, const void* q_proj, int io_dty
                     int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq,
                     int k_bits, int v_bits, int use_qjl, int chunk_pages, tq_stream_t stream);
 
+#define TQ_DECODE_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+
+/* tq_decode_paged for callers that cannot provide a workspace.  It has no
+ * counterpart in the reference.  Meant for hosts that cannot allocate device
+ * memory themselves: a server that gave all free HBM to its KV-cache pool at
+ * start-up, so any later allocation fails, or a foreign-language binding that
+ * only passes on pointers it received.  Same arguments as tq_decode_paged
+ * without workspace / workspace_bytes; the split-K partials go to a fixed
+ * 16 MiB array that is part of the library image (every GPU that loads the
+ * library holds those 16 MiB until the process exits).  Problems that need
+ * more (tq_decode_workspace_bytes(...) > TQ_DECODE_STATIC_SCRATCH_BYTES)
+ * are refused with TQ_ERR_WORKSPACE before anything is launched: pass a
+ * larger chunk_pages or use tq_decode_paged.  The function calls no
+ * allocation routine.  The first call on each device looks up the device
+ * address of the array (cudaGetSymbolAddress) and remembers it; make that
+ * first call during set-up, before any stream capture begins.  All calls on
+ * a device share the one array, which keeps whatever the last call left in it
+ * (nothing in it needs clearing: each call writes every partial it later
+ * reads); two calls whose kernels overlap on the GPU, e.g. on different
+ * streams, race on it and must be serialised by the caller. */
+int tq_decode_paged_static(void* out, const void* q_rot, const void* q_proj, int io_dtype,
+                           const void* cache, int64_t num_blocks, int block_size,
+                           const int32_t* block_tables, int64_t bt_stride, const int32_t* seq_lens,
+                           const float* k_centroids, const float* v_centroids,
+                           float sm_scale, float corr_scale, float sparse_thresh,
+                           int32_t* status, uint32_t* skip_stats,
+                           int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq,
+                           int k_bits, int v_bits, int use_qjl, int chunk_pages, tq_stream_t stream);
+
 /* Fast Walsh-Hadamard rotation of n rows of 128 values: out = scale * (in @ H).
  * Used for q' = q H before decode and out = o H after it, the two matmuls of
  * TurboQuantFP8State.rotate_query / rotate_output

@@ -781,3 +781,67 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     }
     return TQ_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode without a caller-provided workspace.
+//
+// Some hosts of this library have no way to obtain device memory of their own: an inference
+// server that hands every free byte of HBM to its KV-cache pool at start-up (a later cudaMalloc
+// simply fails), or a binding in a runtime that only forwards pointers it was given and owns no
+// device allocator.  For them the split-K scratch lives in a fixed array inside the library image,
+// reserved on every GPU that loads the library for as long as the process runs.
+// ---------------------------------------------------------------------------------------------
+namespace tq {
+namespace {
+
+constexpr size_t kStaticScratchBytes = TQ_DECODE_STATIC_SCRATCH_BYTES;   // 16 MiB, the stated limit
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// In host code `g_decode_scratch` is only a handle for the runtime, not a device address: the
+// address a kernel may use comes from cudaGetSymbolAddress, asked once per device.
+void* static_scratch_address(int* status) {
+    static void* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        *status = TQ_ERR_LAUNCH;
+        return nullptr;
+    }
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_decode_scratch) != cudaSuccess || !ptr) {
+            *status = TQ_ERR_LAUNCH;
+            return nullptr;
+        }
+        cached[dev] = ptr;
+    }
+    *status = TQ_OK;
+    return cached[dev];
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" int tq_decode_paged_static(void* out, const void* q_rot, const void* q_proj, int io_dtype, const void* cache,
+                                      int64_t num_blocks, int block_size, const int32_t* block_tables,
+                                      int64_t bt_stride, const int32_t* seq_lens, const float* k_centroids,
+                                      const float* v_centroids, float sm_scale, float corr_scale, float sparse_thresh,
+                                      int32_t* status, uint32_t* skip_stats, int num_seqs, int num_q_heads,
+                                      int num_kv_heads, int max_pages_per_seq, int k_bits, int v_bits, int use_qjl,
+                                      int chunk_pages, tq_stream_t stream) {
+    if (num_seqs == 0) return TQ_OK;
+    if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    if (chunk_pages <= 0) chunk_pages = tq_decode_auto_chunk_pages(num_seqs, num_kv_heads, num_q_heads, max_pages_per_seq);
+    // Refuse, before touching the GPU, any problem whose split-K partials do not fit the fixed array.
+    const int64_t need = tq_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, max_pages_per_seq, chunk_pages);
+    if (need < 0) return static_cast<int>(need);
+    if (need > static_cast<int64_t>(tq::kStaticScratchBytes)) return TQ_ERR_WORKSPACE;
+    int rc = TQ_OK;
+    void* scratch = tq::static_scratch_address(&rc);
+    if (rc != TQ_OK) return rc;
+    // Nothing in the scratch has to start at zero: every partial a merge reads was written by the
+    // partial kernel of the same call, so contents left by an earlier call are never observed.
+    return tq_decode_paged(out, q_rot, q_proj, io_dtype, cache, num_blocks, block_size, block_tables, bt_stride,
+                           seq_lens, k_centroids, v_centroids, sm_scale, corr_scale, sparse_thresh, scratch,
+                           static_cast<int64_t>(tq::kStaticScratchBytes), status, skip_stats, num_seqs, num_q_heads,
+                           num_kv_heads, max_pages_per_seq, k_bits, v_bits, use_qjl, chunk_pages, stream);
+}
