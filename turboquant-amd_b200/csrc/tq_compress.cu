@@ -1,43 +1,89 @@
 // KV compression for sm_100a: fast WHT, norm, Lloyd-Max bucketize, QJL signs, bit-packing.
 //
-// One warp compresses one 128-value vector; lane l holds dims 4l..4l+3.  The
-// 128-point Walsh-Hadamard transform is two in-register butterfly stages and
-// five warp-shuffle stages.  Everything after the rotation follows
-// polarquant_compress of the reference (turboquant/core/quantizer.py:141-173)
-// operation by operation in fp32:
+// Four lanes compress one 128-value vector: lane j of a group holds the 32 dims 32 j .. 32 j + 31
+// in registers, a warp works on 8 vectors at a time (first the keys of 8 (token, head) items, then
+// their values).  The 128-point Walsh-Hadamard transform is five butterfly stages inside the lane
+// and two warp-shuffle stages across the four lanes, so only 2 of 7 stages pay for a shuffle, and
+// every per-vector scalar (norm, square root, reciprocal) is amortised over 32 elements per lane.
+// A lane's 32 dims are exactly one quarter of a K record of the paged cache, so the packed words
+// are assembled in registers and written with one 16-byte store; no cross-lane reduction is needed.
+//
+// Everything after the rotation follows polarquant_compress of the reference
+// (turboquant/core/quantizer.py:141-173) operation by operation in fp32:
 //   n = sqrt(sum r^2);  u = r / (n + 1e-8);  idx = #{j : b_j < u};
 //   e = (u - c[idx]) * n;  rn = sqrt(sum e^2);  sign = (e >= 0).
-// The packed fields are then written either into the paged cache (layout of
-// turboquant/kernels/paged_layout.py) or into the contiguous arrays of
-// compress_k / compress_v (turboquant/kernels/packed_compress.py:157-240).
+// The division is done as a correctly rounded reciprocal followed by one Newton-style correction
+// of each quotient (q0 = r * inv; q = q0 + (r - q0 * den) * inv), which returns the IEEE quotient.
+// Outputs go either into the paged cache (layout of turboquant/kernels/paged_layout.py) or into
+// the contiguous arrays of compress_k / compress_v (turboquant/kernels/packed_compress.py:157-240).
 #include "tq_common.cuh"
 
 namespace tq {
 namespace {
 
 constexpr int kWarpsPerCta = 4;
+constexpr int kItemsPerWarp = 8;
+constexpr int kItemsPerCta = kWarpsPerCta * kItemsPerWarp;
 
-// ---- 128-point WHT across a warp (unnormalised) -------------------------------------
-__device__ __forceinline__ void fwht128(float (&x)[4], int lane) {
-    float a = x[0] + x[1], b = x[0] - x[1], c = x[2] + x[3], d = x[2] - x[3];
-    x[0] = a + c; x[1] = b + d; x[2] = a - c; x[3] = b - d;
+// ---- loads: 32 consecutive elements of one row as fp32 ---------------------------------------
+__device__ __forceinline__ void load32(const void* base, int64_t elem_off, int dtype, float (&x)[32]) {
+    if (dtype == TQ_DTYPE_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
 #pragma unroll
-    for (int m = 1; m < 32; m <<= 1) {
-        const float sgn = (lane & m) ? -1.f : 1.f;
+        for (int i = 0; i < 8; ++i) {
+            const float4 v = __ldg(p + i);
+            x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+        }
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem_off);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[e], m);
-            x[e] = fmaf(sgn, x[e], other);
+        for (int i = 0; i < 4; ++i) {
+            const uint4 v = __ldg(p + i);
+            const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (dtype == TQ_DTYPE_F16) {
+                    const float2 t = unpack_half2(r[k]);
+                    x[8 * i + 2 * k] = t.x;
+                    x[8 * i + 2 * k + 1] = t.y;
+                } else {
+                    x[8 * i + 2 * k] = __uint_as_float(r[k] << 16);
+                    x[8 * i + 2 * k + 1] = __uint_as_float(r[k] & 0xffff0000u);
+                }
+            }
         }
     }
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
+// ---- 128-point WHT over a group of 4 lanes (unnormalised) ---------------------------------------
+__device__ __forceinline__ void fwht128(float (&x)[32], int lane) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (!(i & h)) {
+                const float a = x[i], b = x[i + h];
+                x[i] = a + b;
+                x[i + h] = a - b;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1) {
+        const float sgn = (lane & m) ? -1.f : 1.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = fmaf(sgn, x[i], __shfl_xor_sync(0xffffffffu, x[i], m));
+    }
+}
+
+__device__ __forceinline__ float group_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
     return v;
 }
 
+// ---- bucketize: idx = number of boundaries strictly below u (searchsorted, right=False) -----------
+// Branch-free binary search over boundaries held in registers; every index is a compile-time constant.
 template <int BITS>
 struct Boundaries {
     float b[(1 << BITS) - 1];
@@ -45,147 +91,155 @@ struct Boundaries {
 #pragma unroll
         for (int i = 0; i < (1 << BITS) - 1; ++i) b[i] = __ldg(g + i);
     }
-    // searchsorted(right=False): number of boundaries strictly below u; ties go down.
     __device__ __forceinline__ int bucket(float u) const {
-        int idx = 0;
-#pragma unroll
-        for (int i = 0; i < (1 << BITS) - 1; ++i) idx += (u > b[i]) ? 1 : 0;
-        return idx;
+        if constexpr (BITS == 2) {
+            const bool p1 = u > b[1];
+            const bool p0 = u > (p1 ? b[2] : b[0]);
+            return (p1 ? 2 : 0) + (p0 ? 1 : 0);
+        } else if constexpr (BITS == 3) {
+            const bool p2 = u > b[3];
+            const bool p1 = u > (p2 ? b[5] : b[1]);
+            const float hi = p2 ? b[6] : b[2], lo = p2 ? b[4] : b[0];
+            const bool p0 = u > (p1 ? hi : lo);
+            return (p2 ? 4 : 0) + (p1 ? 2 : 0) + (p0 ? 1 : 0);
+        } else {
+            const bool p3 = u > b[7];
+            const bool p2 = u > (p3 ? b[11] : b[3]);
+            const float h1 = p3 ? b[13] : b[5], l1 = p3 ? b[9] : b[1];
+            const bool p1 = u > (p2 ? h1 : l1);
+            const float c3 = p3 ? b[14] : b[6], c2 = p3 ? b[12] : b[4], c1 = p3 ? b[10] : b[2], c0 = p3 ? b[8] : b[0];
+            const float hh = p2 ? c3 : c1, ll = p2 ? c2 : c0;
+            const bool p0 = u > (p1 ? hh : ll);
+            return (p3 ? 8 : 0) + (p2 ? 4 : 0) + (p1 ? 2 : 0) + (p0 ? 1 : 0);
+        }
     }
 };
 
-struct Quantized {
-    int idx[4];
-    uint32_t sign4;   // bit e = 1 when the residual of element e is >= 0
+// Result of compressing one quarter (32 dims) of a vector; norm and rnorm are whole-vector values.
+struct Quarter {
+    uint32_t idx[32];
+    uint32_t signs;   // bit l = 1 when the residual of local dim l is >= 0
     float norm, rnorm;
-    float u[4];       // normalised rotated coordinates (kept for the unpacked output mode)
 };
 
-// x: 4 raw values of this lane.  csm: centroids in shared memory (only read when QJL).
+// x: this lane's 32 values.  csm: centroids in shared memory (read only when QJL).
 template <int BITS, bool QJL>
-__device__ __forceinline__ void quantize_vec(float (&x)[4], bool rotate, int lane, const Boundaries<BITS>& bd,
-                                             const float* csm, Quantized& q) {
+__device__ __forceinline__ void quantize_quarter(float (&x)[32], bool rotate, int lane, const Boundaries<BITS>& bd,
+                                                 const float* csm, Quarter& q) {
     if (rotate) {
         fwht128(x, lane);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) x[e] *= kWhtScale;
+        for (int i = 0; i < 32; ++i) x[i] *= kWhtScale;
     }
-    float ss = x[0] * x[0];
-    ss = fmaf(x[1], x[1], ss);
-    ss = fmaf(x[2], x[2], ss);
-    ss = fmaf(x[3], x[3], ss);
-    ss = warp_sum(ss);
-    const float n = sqrtf(ss);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        s0 = fmaf(x[i], x[i], s0);
+        s1 = fmaf(x[i + 1], x[i + 1], s1);
+        s2 = fmaf(x[i + 2], x[i + 2], s2);
+        s3 = fmaf(x[i + 3], x[i + 3], s3);
+    }
+    const float n = sqrtf(group_sum((s0 + s1) + (s2 + s3)));
     const float den = n + 1e-8f;
-    float rs = 0.f;
+    const float inv = __frcp_rn(den);
+    float r0 = 0.f, r1 = 0.f;
     uint32_t sb = 0;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const float u = __fdiv_rn(x[e], den);
-        const int i = bd.bucket(u);
-        q.idx[e] = i;
-        q.u[e] = u;
+    for (int i = 0; i < 32; ++i) {
+        const float q0 = x[i] * inv;
+        const float u = fmaf(fmaf(-q0, den, x[i]), inv, q0);   // = x / den, correctly rounded
+        const int k = bd.bucket(u);
+        q.idx[i] = static_cast<uint32_t>(k);
         if constexpr (QJL) {
-            const float r = (u - csm[i]) * n;
-            rs = fmaf(r, r, rs);
-            sb |= (r >= 0.f ? 1u : 0u) << e;   // -0.0 and +0.0 both count as +
+            const float r = (u - csm[k]) * n;
+            if (i & 1) r1 = fmaf(r, r, r1);
+            else r0 = fmaf(r, r, r0);
+            sb |= (r >= 0.f ? 1u : 0u) << i;   // -0.0 and +0.0 both count as +
         }
     }
-    q.sign4 = sb;
+    q.signs = sb;
     q.norm = n;
-    if constexpr (QJL) q.rnorm = sqrtf(warp_sum(rs));
-    else q.rnorm = 0.f;
+    q.rnorm = QJL ? sqrtf(group_sum(r0 + r1)) : 0.f;
 }
 
-__device__ __forceinline__ uint32_t nibbles4(const int (&i)[4]) {
-    return static_cast<uint32_t>(i[0]) | (static_cast<uint32_t>(i[1]) << 4) | (static_cast<uint32_t>(i[2]) << 8) |
-           (static_cast<uint32_t>(i[3]) << 12);
-}
-
-// Bit b of each of the 4 indices, placed at the top bit of nibbles 0..3.
-__device__ __forceinline__ uint32_t hole_bits(const int (&i)[4], int b) {
-    uint32_t r = 0;
+// ---- paged stores (bit positions: turboquant/kernels/paged_layout.py) ------------------------------
+// K: a lane's 32 dims are one quarter sub-record: BITS index words (+ the sign word).
+template <int BITS>
+__device__ __forceinline__ void pack_k_quarter(const uint32_t (&idx)[32], uint32_t (&w)[BITS]) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) r |= ((static_cast<uint32_t>(i[e]) >> b) & 1u) << (4 * e + 3);
-    return r;
-}
-
-// ---- paged stores -----------------------------------------------------------------------
-// K sub-record words of this lane's dim quarter (lane = 8 * quarter + c).
-template <int BITS, bool QJL>
-__device__ __forceinline__ void store_k_paged(uint8_t* page, int t, int lane, const Quantized& q) {
-    constexpr int NW = BITS + (QJL ? 1 : 0);
-    constexpr int RK = 16 * NW;
-    const int quarter = lane >> 3, c = lane & 7;
-    const uint32_t gmask = 0xffu << (8 * quarter);
-    uint32_t w[NW];
-    const uint32_t f = nibbles4(q.idx);
+    for (int j = 0; j < BITS; ++j) w[j] = 0;
 #pragma unroll
-    for (int j = 0; j < BITS; ++j) {
-        uint32_t v = 0;
+    for (int l = 0; l < 32; ++l) {
+        const int c = l >> 2, e = l & 3;
         if constexpr (BITS == 4) {
-            if (j == (c >> 1)) v = f << (16 * (c & 1));
+            w[c >> 1] |= idx[l] << ((c & 1) * 16 + 4 * e);
         } else if constexpr (BITS == 3) {
             if (c < 6) {
-                if (j == (c >> 1)) v = f << (16 * (c & 1));
+                w[c >> 1] |= idx[l] << ((c & 1) * 16 + 4 * e);
             } else {
-                v = hole_bits(q.idx, j) << (16 * (c - 6));
+#pragma unroll
+                for (int b = 0; b < 3; ++b) w[b] |= ((idx[l] >> b) & 1u) << ((c - 6) * 16 + 4 * e + 3);
             }
         } else {
-            if (j == (c >> 2)) v = (f << (2 * ((c >> 1) & 1))) << (16 * (c & 1));
+            w[c >> 2] |= idx[l] << ((c & 1) * 16 + 4 * e + ((c >> 1) & 1) * 2);
         }
-        w[j] = __reduce_or_sync(gmask, v);
     }
-    if constexpr (QJL) {
-        w[BITS] = __reduce_or_sync(gmask, q.sign4 << (4 * c));   // bit l = sign of dim 32 * quarter + l
-    }
-    if (c == 0) {
-        uint8_t* dst = page + t * RK + quarter * (RK / 4);
-        if constexpr (NW == 4) {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-        } else if constexpr (NW == 2) {
-            *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-        } else {
+}
+
+template <int BITS, bool QJL>
+__device__ __forceinline__ void store_k_paged(uint8_t* page, int t, int quarter, const Quarter& q) {
+    constexpr int NW = BITS + (QJL ? 1 : 0);
+    constexpr int RK = 16 * NW;
+    uint32_t w[BITS];
+    pack_k_quarter<BITS>(q.idx, w);
+    uint8_t* dst = page + t * RK + quarter * (RK / 4);
+    if constexpr (NW == 4) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], QJL ? q.signs : w[BITS - 1]);
+    } else if constexpr (NW == 2) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    } else {
 #pragma unroll
-            for (int j = 0; j < NW; ++j) reinterpret_cast<uint32_t*>(dst)[j] = w[j];
-        }
+        for (int j = 0; j < BITS; ++j) reinterpret_cast<uint32_t*>(dst)[j] = w[j];
+        if constexpr (QJL) reinterpret_cast<uint32_t*>(dst)[BITS] = q.signs;
     }
-    if (lane == 0) {
+    if (quarter == 0) {
         reinterpret_cast<__half*>(page + 16 * RK)[norm_slot(t)] = __float2half_rn(q.norm);
         if constexpr (QJL) reinterpret_cast<__half*>(page + 16 * RK + 32)[norm_slot(t)] = __float2half_rn(q.rnorm);
     }
 }
 
-// V 16-bit fields of this lane's dim group (lane = 4 * g + u).
+// V: a lane's 32 dims are two dim groups g = 2 * quarter + {0, 1}; each gets BITS 16-bit fields.
 template <int BITS>
-__device__ __forceinline__ void store_v_paged(uint8_t* vpart, int t, int lane, const Quantized& q) {
-    const int g = lane >> 2, u = lane & 3;
-    const uint32_t gmask = 0xfu << (4 * g);
-    const uint32_t f = nibbles4(q.idx);
-    uint32_t mine = 0;
+__device__ __forceinline__ void store_v_paged(uint8_t* vpart, int t, int quarter, const Quarter& q) {
+    const int pair = t >> 1, half = t & 1;
 #pragma unroll
-    for (int j = 0; j < BITS; ++j) {
-        uint32_t v = 0;
-        if constexpr (BITS == 4) {
-            if (j == u) v = f;
-        } else if constexpr (BITS == 3) {
-            if (u < 3) {
-                if (j == u) v = f;
+    for (int gg = 0; gg < 2; ++gg) {
+        uint32_t f[BITS];
+#pragma unroll
+        for (int j = 0; j < BITS; ++j) f[j] = 0;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+            const uint32_t i = q.idx[16 * gg + m];
+            const int u = m >> 2, e = m & 3;
+            if constexpr (BITS == 4) {
+                f[u] |= i << (4 * e);
+            } else if constexpr (BITS == 3) {
+                if (u < 3) {
+                    f[u] |= i << (4 * e);
+                } else {
+#pragma unroll
+                    for (int b = 0; b < 3; ++b) f[b] |= ((i >> b) & 1u) << (4 * e + 3);
+                }
             } else {
-                v = hole_bits(q.idx, j);
+                f[u >> 1] |= i << (4 * e + (u & 1) * 2);
             }
-        } else {
-            if (j == (u >> 1)) v = f << (2 * (u & 1));
         }
-        const uint32_t r = __reduce_or_sync(gmask, v);
-        if (j == u) mine = r;
+        const int g = 2 * quarter + gg;
+#pragma unroll
+        for (int j = 0; j < BITS; ++j)
+            *reinterpret_cast<uint16_t*>(vpart + ((j * 8 + pair) * 8 + g) * 4 + half * 2) = static_cast<uint16_t>(f[j]);
     }
-    if (u < BITS) {
-        const int pair = t >> 1;
-        uint8_t* dst = vpart + ((u * 8 + pair) * 8 + g) * 4 + (t & 1) * 2;
-        *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(mine);
-    }
-    if (lane == 0) reinterpret_cast<__half*>(vpart + 256 * BITS)[norm_slot(t)] = __float2half_rn(q.norm);
+    if (quarter == 0) reinterpret_cast<__half*>(vpart + 256 * BITS)[norm_slot(t)] = __float2half_rn(q.norm);
 }
 
 struct PagedParams {
@@ -210,39 +264,56 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compress_paged_kernel(const
     __shared__ float csm[1 << KB];
     if (threadIdx.x < (1 << KB)) csm[threadIdx.x] = p.kc[threadIdx.x];
     __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (item >= p.n_items) return;
-    const int64_t tok = item / p.Hkv;
-    const int head = static_cast<int>(item % p.Hkv);
-    int64_t slot = p.slot_mapping[tok];
-    if (slot < 0) slot = 0;   // the reference clamps padding slots to 0
-    if (slot >= p.num_slots) {
-        if (lane == 0 && p.status) atomicOr(p.status, TQ_STATUS_BAD_SLOT);
-        return;
+    const int lane = threadIdx.x & 31, quarter = lane & 3;
+    const int64_t item = (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2);
+    // Lanes of items past the end still take part in the shuffles (on zeros) and store nothing.
+    bool live = item < p.n_items;
+    int64_t tok = 0;
+    int head = 0, t = 0;
+    uint8_t* page = nullptr;
+    if (live) {
+        tok = item / p.Hkv;
+        head = static_cast<int>(item - tok * p.Hkv);
+        int64_t slot = p.slot_mapping[tok];
+        if (slot < 0) slot = 0;   // the reference clamps padding slots to 0
+        if (slot >= p.num_slots) {
+            if (quarter == 0 && p.status) atomicOr(p.status, TQ_STATUS_BAD_SLOT);
+            live = false;
+        } else {
+            const int64_t blk = slot / p.block_size;
+            const int off = static_cast<int>(slot - blk * p.block_size);
+            const int spb = p.block_size / kPageTokens;
+            page = p.cache + ((blk * p.Hkv + head) * spb + off / kPageTokens) * PAGE;
+            t = off % kPageTokens;
+        }
     }
-    const int64_t blk = slot / p.block_size;
-    const int off = static_cast<int>(slot % p.block_size);
-    const int spb = p.block_size / kPageTokens;
-    uint8_t* page = p.cache + ((blk * p.Hkv + head) * spb + off / kPageTokens) * PAGE;
-    const int t = off % kPageTokens;
-
-    Boundaries<KB> kbd;
-    kbd.load(p.kb);
-    float x[4];
-    Quantized q;
-    load4(p.key, tok * p.ks_t + head * p.ks_h + 4 * lane, p.in_dtype, x);
-    quantize_vec<KB, QJL>(x, p.rotate != 0, lane, kbd, csm, q);
-    store_k_paged<KB, QJL>(page, t, lane, q);
-
-    Boundaries<VB> vbd;
-    vbd.load(p.vb);
-    load4(p.value, tok * p.vs_t + head * p.vs_h + 4 * lane, p.in_dtype, x);
-    quantize_vec<VB, false>(x, p.rotate != 0, lane, vbd, nullptr, q);
-    store_v_paged<VB>(page + KPART, t, lane, q);
+    float x[32];
+    Quarter q;
+    {
+        Boundaries<KB> kbd;
+        kbd.load(p.kb);
+        if (live) load32(p.key, tok * p.ks_t + head * p.ks_h + 32 * quarter, p.in_dtype, x);
+        else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        quantize_quarter<KB, QJL>(x, p.rotate != 0, lane, kbd, csm, q);
+        if (live) store_k_paged<KB, QJL>(page, t, quarter, q);
+    }
+    {
+        Boundaries<VB> vbd;
+        vbd.load(p.vb);
+        if (live) load32(p.value, tok * p.vs_t + head * p.vs_h + 32 * quarter, p.in_dtype, x);
+        else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        quantize_quarter<VB, false>(x, p.rotate != 0, lane, vbd, nullptr, q);
+        if (live) store_v_paged<VB>(page + KPART, t, quarter, q);
+    }
 }
 
-// ---- contiguous outputs ---------------------------------------------------------------------
+// ---- contiguous outputs ---------------------------------------------------------------------------
 enum class OutMode { kPackedK, kPackedV, kUnpacked };
 
 struct ContigParams {
@@ -262,22 +333,25 @@ struct ContigParams {
     int in_dtype, rotate, permute;
 };
 
+// Reference byte layouts: 2-bit 4 per byte LSB first, 4-bit low nibble first, 3-bit little-endian stream.
+// A lane's 32 dims are 8 / 12 / 16 consecutive bytes of the row.
 template <int BITS>
-__device__ __forceinline__ void store_idx_contig(uint8_t* row, int lane, const int (&i)[4]) {
-    if constexpr (BITS == 2) {
-        row[lane] = static_cast<uint8_t>(i[0] | (i[1] << 2) | (i[2] << 4) | (i[3] << 6));
-    } else if constexpr (BITS == 4) {
-        reinterpret_cast<uint16_t*>(row)[lane] = static_cast<uint16_t>(nibbles4(i));
-    } else {
-        // 12 bits per lane; four lanes make 48 bits = 6 bytes of the little-endian stream.
-        const uint32_t mine = i[0] | (i[1] << 3) | (i[2] << 6) | (i[3] << 9);
-        const int base = lane & ~3;
-        const uint32_t a = __shfl_sync(0xffffffffu, mine, base), b = __shfl_sync(0xffffffffu, mine, base + 1);
-        const uint32_t c = __shfl_sync(0xffffffffu, mine, base + 2), d = __shfl_sync(0xffffffffu, mine, base + 3);
-        const uint64_t v = static_cast<uint64_t>(a) | (static_cast<uint64_t>(b) << 12) | (static_cast<uint64_t>(c) << 24) |
-                           (static_cast<uint64_t>(d) << 36);
-        const int k = lane & 3;
-        if (k < 3) reinterpret_cast<uint16_t*>(row + 6 * (lane >> 2))[k] = static_cast<uint16_t>(v >> (16 * k));
+__device__ __forceinline__ void store_idx_contig(uint8_t* row, int quarter, const uint32_t (&idx)[32]) {
+    uint32_t w[BITS];
+#pragma unroll
+    for (int j = 0; j < BITS; ++j) w[j] = 0;
+#pragma unroll
+    for (int l = 0; l < 32; ++l) {
+        const int bit = l * BITS;
+        w[bit >> 5] |= idx[l] << (bit & 31);
+        if ((bit & 31) + BITS > 32) w[(bit >> 5) + 1] |= idx[l] >> (32 - (bit & 31));
+    }
+    uint32_t* dst = reinterpret_cast<uint32_t*>(row + quarter * (4 * BITS));
+    if constexpr (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    else if constexpr (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    else {
+#pragma unroll
+        for (int j = 0; j < BITS; ++j) dst[j] = w[j];
     }
 }
 
@@ -287,60 +361,76 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compress_contig_kernel(cons
     __shared__ float csm[1 << BITS];
     if (threadIdx.x < (1 << BITS)) csm[threadIdx.x] = p.c ? p.c[threadIdx.x] : 0.f;
     __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (row >= p.n) return;
+    const int lane = threadIdx.x & 31, quarter = lane & 3;
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2);
+    const bool live = row < p.n;
     Boundaries<BITS> bd;
     bd.load(p.b);
-    float x[4];
-    Quantized q;
-    load4(p.x, row * kHeadDim + 4 * lane, p.in_dtype, x);
+    float x[32];
+    Quarter q;
+    if (live) load32(p.x, row * kHeadDim + 32 * quarter, p.in_dtype, x);
+    else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = 0.f;
+    }
     if constexpr (MODE == OutMode::kUnpacked) {
-        if (p.signs) quantize_vec<BITS, true>(x, p.rotate != 0, lane, bd, csm, q);
-        else quantize_vec<BITS, false>(x, p.rotate != 0, lane, bd, csm, q);
-        const int64_t o = row * kHeadDim + 4 * lane;
-        float m[4];
+        const bool with_signs = p.signs != nullptr;   // uniform over the grid
+        if (with_signs) quantize_quarter<BITS, true>(x, p.rotate != 0, lane, bd, csm, q);
+        else quantize_quarter<BITS, false>(x, p.rotate != 0, lane, bd, csm, q);
+        if (!live) return;
+        const int64_t o = row * kHeadDim + 32 * quarter;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            p.indices[o + e] = q.idx[e];
-            m[e] = csm[q.idx[e]] * q.norm;
+        for (int i = 0; i < 32; i += 2) {
+            longlong2 v;
+            v.x = q.idx[i];
+            v.y = q.idx[i + 1];
+            *reinterpret_cast<longlong2*>(p.indices + o + i) = v;
         }
-        *reinterpret_cast<float4*>(p.mse + o) = make_float4(m[0], m[1], m[2], m[3]);
-        if (p.signs) {
-            float s[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[e] = ((q.sign4 >> e) & 1u) ? 1.f : -1.f;
-            *reinterpret_cast<float4*>(p.signs + o) = make_float4(s[0], s[1], s[2], s[3]);
+        for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(p.mse + o + i) = make_float4(csm[q.idx[i]] * q.norm, csm[q.idx[i + 1]] * q.norm,
+                                                                   csm[q.idx[i + 2]] * q.norm, csm[q.idx[i + 3]] * q.norm);
+        if (with_signs) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                float s[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[e] = ((q.signs >> (i + e)) & 1u) ? 1.f : -1.f;
+                *reinterpret_cast<float4*>(p.signs + o + i) = make_float4(s[0], s[1], s[2], s[3]);
+            }
         }
-        if (lane == 0) {
+        if (quarter == 0) {
             p.norms[row] = q.norm;
             if (p.rnorm) p.rnorm[row] = q.rnorm;
         }
     } else {
-        quantize_vec<BITS, QJL>(x, p.rotate != 0, lane, bd, csm, q);
-        store_idx_contig<BITS>(p.idx_out + row * (16 * BITS), lane, q.idx);
+        quantize_quarter<BITS, QJL>(x, p.rotate != 0, lane, bd, csm, q);
+        if (!live) return;
+        store_idx_contig<BITS>(p.idx_out + row * (16 * BITS), quarter, q.idx);
         if constexpr (QJL) {
             uint8_t* srow = p.sign_out + row * 16;
             if (p.permute) {
-                // stride-4 order: output bit 32 c + i <- dim c + 4 i, i.e. word c collects element c of every lane
-                uint32_t w[4];
+                // stride-4 order: output bit 32 c + i <- dim c + 4 i.  This lane's dim 32 q + l has
+                // c = l & 3 and i = 8 q + (l >> 2): it fills byte q of each of the four 32-bit words.
 #pragma unroll
-                for (int e = 0; e < 4; ++e) w[e] = __ballot_sync(0xffffffffu, (q.sign4 >> e) & 1u);
-                if (lane == 0) *reinterpret_cast<uint4*>(srow) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v = 0;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v |= ((q.signs >> (4 * k + c)) & 1u) << k;
+                    srow[4 * c + quarter] = static_cast<uint8_t>(v);
+                }
             } else {
-                // sequential: byte j bit b <- dim 8 j + b; two lanes share a byte
-                const uint32_t other = __shfl_xor_sync(0xffffffffu, q.sign4, 1);
-                if (!(lane & 1)) srow[lane >> 1] = static_cast<uint8_t>(q.sign4 | (other << 4));
+                reinterpret_cast<uint32_t*>(srow)[quarter] = q.signs;   // byte j bit b <- dim 8 j + b
             }
-            if (lane == 0) p.rnorm_h[row] = __float2half_rn(q.rnorm);
+            if (quarter == 0) p.rnorm_h[row] = __float2half_rn(q.rnorm);
         }
-        if (lane == 0) p.norm_h[row] = __float2half_rn(q.norm);
+        if (quarter == 0) p.norm_h[row] = __float2half_rn(q.norm);
     }
 }
 
 template <int KB, int VB>
 int launch_paged(const PagedParams& p, bool qjl, cudaStream_t st) {
-    const unsigned grid = static_cast<unsigned>((p.n_items + kWarpsPerCta - 1) / kWarpsPerCta);
+    const unsigned grid = static_cast<unsigned>((p.n_items + kItemsPerCta - 1) / kItemsPerCta);
     if (qjl) compress_paged_kernel<KB, VB, true><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
     else compress_paged_kernel<KB, VB, false><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
@@ -358,7 +448,7 @@ int launch_paged_v(const PagedParams& p, int vb, bool qjl, cudaStream_t st) {
 
 template <OutMode MODE>
 int launch_contig(const ContigParams& p, int bits, cudaStream_t st) {
-    const unsigned grid = static_cast<unsigned>((p.n + kWarpsPerCta - 1) / kWarpsPerCta);
+    const unsigned grid = static_cast<unsigned>((p.n + kItemsPerCta - 1) / kItemsPerCta);
     switch (bits) {
         case 2: compress_contig_kernel<2, MODE><<<grid, kWarpsPerCta * 32, 0, st>>>(p); break;
         case 3: compress_contig_kernel<3, MODE><<<grid, kWarpsPerCta * 32, 0, st>>>(p); break;
@@ -373,7 +463,6 @@ int elem_bytes(int d) { return d == TQ_DTYPE_F32 ? 4 : 2; }
 
 }  // namespace
 }  // namespace tq
-
 using namespace tq;
 
 extern "C" int tq_version(void) { return (0 << 16) | 1; }
@@ -396,11 +485,11 @@ extern "C" int tq_compress_paged(const void* key, const void* value, int in_dtyp
     if (!dtype_ok(in_dtype)) return TQ_ERR_UNSUPPORTED;
     if (block_size <= 0 || block_size % kPageTokens) return TQ_ERR_UNSUPPORTED;
     if (k_bits < 2 || k_bits > 4 || v_bits < 2 || v_bits > 4) return TQ_ERR_UNSUPPORTED;
-    const int align_elems = 4;  // each lane loads 4 consecutive elements with one vector load
+    const int align_elems = 16 / elem_bytes(in_dtype);  // lanes read rows with 16-byte vector loads
     if (k_stride_token % align_elems || k_stride_head % align_elems || v_stride_token % align_elems ||
         v_stride_head % align_elems)
         return TQ_ERR_ARG;
-    const uintptr_t amask = static_cast<uintptr_t>(4 * elem_bytes(in_dtype) - 1);
+    const uintptr_t amask = 15;
     if ((reinterpret_cast<uintptr_t>(key) & amask) || (reinterpret_cast<uintptr_t>(value) & amask) ||
         (reinterpret_cast<uintptr_t>(cache) & 15))
         return TQ_ERR_ARG;
