@@ -24,10 +24,19 @@
 namespace tq {
 namespace {
 
-constexpr int kWarps = 4;
+#ifndef TQ_DEC_WARPS
+#define TQ_DEC_WARPS 4
+#endif
+#ifndef TQ_DEC_STAGES
+#define TQ_DEC_STAGES 4
+#endif
+#ifndef TQ_DEC_MINBLOCKS
+#define TQ_DEC_MINBLOCKS 4
+#endif
+constexpr int kWarps = TQ_DEC_WARPS;
 constexpr int kThreads = kWarps * 32;
 constexpr int kOPad = 132;  // row stride of the merge buffer (floats)
-constexpr int kStages = 4;  // pages in flight per warp
+constexpr int kStages = TQ_DEC_STAGES;  // pages in flight per warp
 constexpr int kBarBytes = kWarps * 2 * kStages * 8;  // mbarriers at the start of dynamic shared memory
 
 struct DecodeParams {
@@ -259,7 +268,7 @@ __device__ __forceinline__ void load_q_frag(const void* q, int64_t row_off, int 
 }
 
 template <int KB, int VB, bool QJL, bool SPARSE, int NSTAGE>
-__global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_kernel(const DecodeParams p) {
     constexpr int NWK = KB + (QJL ? 1 : 0);
     constexpr int RK = 16 * NWK;
     constexpr int KN_OFF = 16 * RK;
@@ -585,7 +594,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_partial_kernel(const Decod
     const int dim = threadIdx.x;
     const int col = dim + (dim >> 5);
     const int nchunks = (npages + p.chunk_pages - 1) / p.chunk_pages;
-    for (int g = 0; g < nq; ++g) {
+    for (int g = 0; g < (dim < kHeadDim ? nq : 0); ++g) {
         float M = sm_m[0][g];
 #pragma unroll
         for (int w = 1; w < kWarps; ++w) M = fmaxf(M, sm_m[w][g]);
@@ -669,9 +678,11 @@ int dispatch_flags(const DecodeParams& p, bool qjl, bool sparse, dim3 grid, cuda
 template <int KB>
 int dispatch_v(const DecodeParams& p, int vb, bool qjl, bool sparse, dim3 grid, cudaStream_t stream) {
     switch (vb) {
+#ifndef TQ_DEC_QUICK
         case 2: return dispatch_flags<KB, 2>(p, qjl, sparse, grid, stream);
-        case 3: return dispatch_flags<KB, 3>(p, qjl, sparse, grid, stream);
         case 4: return dispatch_flags<KB, 4>(p, qjl, sparse, grid, stream);
+#endif
+        case 3: return dispatch_flags<KB, 3>(p, qjl, sparse, grid, stream);
     }
     return TQ_ERR_UNSUPPORTED;
 }
@@ -769,9 +780,11 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     int rc;
     switch (k_bits) {
+#ifndef TQ_DEC_QUICK
         case 2: rc = dispatch_v<2>(p, v_bits, qjl, sparse, grid, st); break;
-        case 3: rc = dispatch_v<3>(p, v_bits, qjl, sparse, grid, st); break;
         case 4: rc = dispatch_v<4>(p, v_bits, qjl, sparse, grid, st); break;
+#endif
+        case 3: rc = dispatch_v<3>(p, v_bits, qjl, sparse, grid, st); break;
         default: return TQ_ERR_UNSUPPORTED;
     }
     if (rc != TQ_OK) return rc;
