@@ -60,6 +60,28 @@ def make_lengths(spec: str, batch: int, seed: int) -> torch.Tensor:
     raise ValueError(spec)
 
 
+def shard_heads(hq: int, hkv: int, rank: int, world: int):
+    """KV heads [lo, hi) and query heads [qlo, qhi) owned by `rank`: contiguous head-major slices, no overlap."""
+    if hkv % world:
+        raise SystemExit(f"--gpus {world} must divide the {hkv} KV heads")
+    per = hkv // world
+    g = hq // hkv
+    return per * rank, per * (rank + 1), g * per * rank, g * per * (rank + 1)
+
+
+def make_block_tables(pages: torch.Tensor, seed: int = 99) -> torch.Tensor:
+    """Random placement of every sequence's pages in one shared pool (identical on every rank)."""
+    num_blocks = int(pages.sum())
+    perm = torch.randperm(num_blocks, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
+    bt = torch.zeros(len(pages), int(pages.max()), dtype=torch.int32)
+    o = 0
+    for s in range(len(pages)):
+        n = int(pages[s])
+        bt[s, :n] = perm[o:o + n]
+        o += n
+    return bt
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
@@ -120,10 +142,9 @@ class Workload:
         self.books = Codebooks(self.fmt, device)
         self.block_size = 16
         self.batch = w["batch"]
-        if w["hkv"] % world:
-            raise SystemExit(f"--gpus {world} must divide the {w['hkv']} KV heads")
-        self.hkv = w["hkv"] // world            # this rank's KV heads
-        self.hq = w["hq"] // world
+        lo, hi, qlo, qhi = shard_heads(w["hq"], w["hkv"], rank, world)
+        self.hkv = hi - lo                      # this rank's KV heads
+        self.hq = qhi - qlo
         self.layers = layers_override or w["layers"]
         self.sparse = w["sparse"]
         self.lens = make_lengths(w["lens"], self.batch, seed=1234)
@@ -133,15 +154,7 @@ class Workload:
         self.tok_heads_rank = int(self.lens.sum()) * self.hkv
         self.tok_heads_total = int(self.lens.sum()) * w["hkv"]
         self.bytes_per_tok_head = self.fmt.page_bytes / 16
-        g = torch.Generator().manual_seed(99)
-        perm = torch.randperm(self.num_blocks, generator=g).to(torch.int32)     # shared pool, random placement
-        bt = torch.zeros(self.batch, self.max_blocks, dtype=torch.int32)
-        o = 0
-        for s in range(self.batch):
-            n = int(self.pages[s])
-            bt[s, :n] = perm[o:o + n]
-            o += n
-        self.block_tables = bt.to(device)
+        self.block_tables = make_block_tables(self.pages).to(device)
         self.seq_lens = self.lens.to(device)
         self.rank, self.world = rank, world
         self.caches: list[torch.Tensor] = []
@@ -212,8 +225,15 @@ def time_device_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     q_dev = wl.make_queries(7).to(dev)
     outs = torch.empty_like(q_dev)
     stats = torch.zeros(2, dtype=torch.int32, device=dev) if wl.sparse > 0 else None
-    for _ in range(warmup):
+    decode_layers(wl, q_dev, outs, stats)          # sizes the cached workspace before anything is captured
+    torch.cuda.synchronize()
+    # One step (all layers) is captured once in a CUDA graph and replayed: the launcher library allocates
+    # nothing and does not synchronise, so the captured work is exactly the eager work without launch gaps.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
         decode_layers(wl, q_dev, outs, stats)
+    for _ in range(warmup):
+        graph.replay()
     if stats is not None:
         stats.zero_()
     torch.cuda.synchronize()
@@ -221,7 +241,7 @@ def time_device_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        decode_layers(wl, q_dev, outs, stats)
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
     dist_barrier()
