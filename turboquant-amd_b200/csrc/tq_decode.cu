@@ -5,8 +5,9 @@
 // its own producer and consumer: lane 0 streams the next packed pages from HBM
 // into the warp's private shared-memory ring with bulk async copies that
 // complete on mbarriers, the whole warp then
-//   * turns packed indices into fp16 tensor-core fragments with byte-permute
-//     lookups (the codebook lives in four registers),
+//   * turns packed indices into fp16 tensor-core fragments: a masked byte of the packed word is
+//     the pair index of two neighbouring dims and addresses a lane-replicated half2 table in
+//     shared memory (one byte-extract, one multiply-add, one conflict-free shared load per pair),
 //   * scores 16 tokens x 8 query heads with mma.m16n8k16 (tokens on M, the GQA
 //     group on N), a second MMA chain for the +-1 QJL sign term,
 //   * runs the online softmax on the accumulator fragment,
@@ -62,118 +63,57 @@ struct DecodeParams {
     int64_t block_stride;    // bytes between consecutive blocks of the cache
     int chunk_pages, max_chunks;
     int io_dtype;
+    int share_tables;        // K and V use the same codebook: one pair table serves both
 };
 
 // ---------------------------------------------------------------------------------
-// Codebook tables in registers: byte k of L[] / H[] is the low / high byte of fp16(c[k]).
+// Pair lookup table in shared memory.  After masking, every byte of an index word holds the
+// indices of two neighbouring dims of one token in its two nibbles; that byte addresses a table
+// of half2(c[i0], c[i1]) which is replicated per lane (entry stride 128 bytes, lane l reads
+// word l of an entry) so that a warp's 32 lookups never collide on a bank.  One byte-extract
+// (ALU), one multiply-add for the address (FMA pipe) and one shared load replace the two table
+// permutes and the interleave permute of the register-only path: the logic pipe is the
+// bottleneck of this kernel, the load/store pipe is not.
 // ---------------------------------------------------------------------------------
 template <int BITS>
-struct Lut {
-    static constexpr int N = (1 << BITS) >= 4 ? (1 << BITS) / 4 : 1;
-    uint32_t L[N];
-    uint32_t H[N];
-    __device__ __forceinline__ void build(const float* __restrict__ c) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) {
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int k = i * 4 + j;
-                const uint32_t h = (k < (1 << BITS)) ? __half_as_ushort(__float2half_rn(__ldg(c + k))) : 0u;
-                lo |= (h & 0xffu) << (8 * j);
-                hi |= (h >> 8) << (8 * j);
-            }
-            L[i] = lo;
-            H[i] = hi;
-        }
-    }
-    // sel: four nibbles (low 16 bits) holding indices of elements e0..e3.
-    // r0 = half2(c[e0], c[e1]), r1 = half2(c[e2], c[e3]).
-    __device__ __forceinline__ void lookup(uint32_t sel, uint32_t& r0, uint32_t& r1) const {
-        uint32_t lo4, hi4;
-        if constexpr (BITS == 2) {
-            lo4 = prmt(L[0], L[0], sel);
-            hi4 = prmt(H[0], H[0], sel);
-        } else if constexpr (BITS == 3) {
-            lo4 = prmt(L[0], L[1], sel);
-            hi4 = prmt(H[0], H[1], sel);
-        } else {
-            // 16 entries: look up in both halves of the table, pick per byte by bit 3 of the nibble.
-            const uint32_t s7 = sel & 0x7777u;
-            const uint32_t m = prmt(sel << 4, sel, 0xD9C8u);  // 0xff where the nibble's top bit is set
-            const uint32_t la = prmt(L[0], L[1], s7), lb = prmt(L[2], L[3], s7);
-            const uint32_t ha = prmt(H[0], H[1], s7), hb = prmt(H[2], H[3], s7);
-            lo4 = (la & ~m) | (lb & m);
-            hi4 = (ha & ~m) | (hb & m);
-        }
-        r0 = prmt(lo4, hi4, 0x5140u);
-        r1 = prmt(lo4, hi4, 0x7362u);
-    }
-};
-
-// Selectors for the 8 groups of 4 elements packed in BITS words (see paged_layout.py).
+__host__ __device__ constexpr int lut_entries() { return BITS == 2 ? 64 : (BITS == 3 ? 128 : 256); }
 template <int BITS>
-__device__ __forceinline__ void selectors(const uint32_t (&w)[BITS], uint32_t (&sel)[8]) {
+__host__ __device__ constexpr int lut_bytes() { return lut_entries<BITS>() * 128; }
+
+template <int BITS>
+__device__ __forceinline__ void fill_pair_lut(uint32_t* tab, const float* __restrict__ c, int warp, int lane) {
+    for (int b = warp; b < lut_entries<BITS>(); b += kWarps) {
+        const int i0 = b & 15, i1 = b >> 4;
+        if (i0 < (1 << BITS) && i1 < (1 << BITS))
+            tab[b * 32 + lane] = pack_half2(__half2float(__float2half_rn(__ldg(c + i0))), __half2float(__float2half_rn(__ldg(c + i1))));
+    }
+}
+
+// Words whose bytes are pair indices; word order matches the 8 groups of 4 elements (2 bytes each).
+template <int BITS>
+__device__ __forceinline__ void masked_words(const uint32_t (&w)[BITS], uint32_t (&mw)[4]) {
     if constexpr (BITS == 4) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            sel[2 * j] = w[j];
-            sel[2 * j + 1] = w[j] >> 16;
-        }
+        for (int j = 0; j < 4; ++j) mw[j] = w[j];
     } else if constexpr (BITS == 3) {
 #pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            const uint32_t m = w[j] & 0x77777777u;
-            sel[2 * j] = m;
-            sel[2 * j + 1] = m >> 16;
-        }
-        const uint32_t h = ((w[0] >> 3) & 0x11111111u) | ((w[1] >> 2) & 0x22222222u) | ((w[2] >> 1) & 0x44444444u);
-        sel[6] = h;
-        sel[7] = h >> 16;
+        for (int j = 0; j < 3; ++j) mw[j] = w[j] & 0x77777777u;
+        mw[3] = ((w[0] >> 3) & 0x11111111u) | ((w[1] >> 2) & 0x22222222u) | ((w[2] >> 1) & 0x44444444u);
     } else {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const uint32_t a = w[j] & 0x33333333u;
-            const uint32_t b = (w[j] >> 2) & 0x33333333u;
-            sel[4 * j] = a;
-            sel[4 * j + 1] = a >> 16;
-            sel[4 * j + 2] = b;
-            sel[4 * j + 3] = b >> 16;
+            mw[2 * j] = w[j] & 0x33333333u;
+            mw[2 * j + 1] = (w[j] >> 2) & 0x33333333u;
         }
     }
 }
 
-// For a V pair word (token a in the low halves, token b in the high halves) the same
-// masks give a's selector in the low 16 bits and b's in the high 16 bits.
-template <int BITS>
-__device__ __forceinline__ void pair_selectors(const uint32_t (&w)[BITS], uint32_t (&sa)[4], uint32_t (&sb)[4]) {
-    if constexpr (BITS == 4) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            sa[u] = w[u];
-            sb[u] = w[u] >> 16;
-        }
-    } else if constexpr (BITS == 3) {
-#pragma unroll
-        for (int u = 0; u < 3; ++u) {
-            const uint32_t m = w[u] & 0x77777777u;
-            sa[u] = m;
-            sb[u] = m >> 16;
-        }
-        const uint32_t h = ((w[0] >> 3) & 0x11111111u) | ((w[1] >> 2) & 0x22222222u) | ((w[2] >> 1) & 0x44444444u);
-        sa[3] = h;
-        sb[3] = h >> 16;
-    } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint32_t a = w[j] & 0x33333333u;
-            const uint32_t b = (w[j] >> 2) & 0x33333333u;
-            sa[2 * j] = a;
-            sb[2 * j] = a >> 16;
-            sa[2 * j + 1] = b;
-            sb[2 * j + 1] = b >> 16;
-        }
-    }
+// half2(c[i0], c[i1]) for byte k of a masked word; lane_base = shared address of the table + 4 * lane.
+__device__ __forceinline__ uint32_t lut_pair(uint32_t lane_base, uint32_t mw, int k) {
+    const uint32_t x = prmt(mw, 0u, 0x4440u | static_cast<uint32_t>(k));
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lane_base + x * 128u));
+    return v;
 }
 
 // QJL sign term on fp16 tensor cores with one logic op per pair of signs.
@@ -279,7 +219,9 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                 // [kWarps][2 * NSTAGE]
-    uint8_t* ring = smem + kBarBytes;                                   // [kWarps][NSTAGE][PAGE]
+    uint32_t* tabk = reinterpret_cast<uint32_t*>(smem + kBarBytes);     // pair table of the K codebook
+    uint32_t* tabv = p.share_tables ? tabk : tabk + lut_bytes<KB>() / 4;
+    uint8_t* ring = smem + kBarBytes + lut_bytes<KB>() + (p.share_tables ? 0 : lut_bytes<VB>());  // [kWarps][NSTAGE][PAGE]
     float* sm_o = reinterpret_cast<float*>(ring);                       // reused after the page loop
     __shared__ float sm_m[kWarps][8];
     __shared__ float sm_l[kWarps][8];
@@ -319,10 +261,10 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     __syncwarp();
 
     // ---- per-warp constants: codebooks and query fragments --------------------------
-    Lut<KB> klut;
-    Lut<VB> vlut;
-    klut.build(p.kc);
-    vlut.build(p.vc);
+    fill_pair_lut<KB>(tabk, p.kc, warp, lane);
+    if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
+    __syncthreads();
+    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
     uint32_t qf[16], qpf[QJL ? 16 : 1];
     float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
     {
@@ -416,21 +358,20 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         uint32_t wa[NWK], wb[NWK];
         lds_words<NWK>(pg + lane * (NWK * 4), wa);
         lds_words<NWK>(pg + (lane + 32) * (NWK * 4), wb);
-        uint32_t sela[8], selb[8];
+        uint32_t mwa[4], mwb[4];
         {
             uint32_t ia[KB], ib[KB];
 #pragma unroll
             for (int i = 0; i < KB; ++i) { ia[i] = wa[i]; ib[i] = wb[i]; }
-            selectors<KB>(ia, sela);
-            selectors<KB>(ib, selb);
+            masked_words<KB>(ia, mwa);
+            masked_words<KB>(ib, mwb);
         }
         float sm[4] = {0.f, 0.f, 0.f, 0.f};
         float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            uint32_t a0, a1, b0, b1;
-            klut.lookup(sela[c], a0, a1);
-            klut.lookup(selb[c], b0, b1);
+            const uint32_t a0 = lut_pair(klut, mwa[c >> 1], 2 * (c & 1)), a1 = lut_pair(klut, mwa[c >> 1], 2 * (c & 1) + 1);
+            const uint32_t b0 = lut_pair(klut, mwb[c >> 1], 2 * (c & 1)), b1 = lut_pair(klut, mwb[c >> 1], 2 * (c & 1) + 1);
             mma_f16_16816(sm, a0, b0, a1, b1, qf[2 * c], qf[2 * c + 1]);
         }
         float sq2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -529,13 +470,12 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 #pragma unroll
                 for (int i = 0; i < VB; ++i)
                     pw[i] = *reinterpret_cast<const uint32_t*>(pg + KPART + ((i * 8 + (4 * o + tig)) * 8 + gid) * 4);
-                uint32_t sa[4], sb[4];
-                pair_selectors<VB>(pw, sa, sb);
+                uint32_t mv[4];
+                masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    uint32_t a0, a1, b0, b1;
-                    vlut.lookup(sa[u], a0, a1);
-                    vlut.lookup(sb[u], b0, b1);
+                    const uint32_t a0 = lut_pair(vlut, mv[u], 0), a1 = lut_pair(vlut, mv[u], 1);
+                    const uint32_t b0 = lut_pair(vlut, mv[u], 2), b1 = lut_pair(vlut, mv[u], 3);
                     mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
                     mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
                 }
@@ -652,7 +592,8 @@ __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const DecodePara
 template <int KB, int VB, bool QJL, bool SPARSE>
 int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     constexpr int PAGE = page_bytes(KB, VB, QJL ? 1 : 0);
-    constexpr size_t smem = kBarBytes + static_cast<size_t>(kWarps) * kStages * PAGE;
+    constexpr size_t smem_max = kBarBytes + lut_bytes<KB>() + lut_bytes<VB>() + static_cast<size_t>(kWarps) * kStages * PAGE;
+    const size_t smem = smem_max - (p.share_tables ? lut_bytes<VB>() : 0);
     static_assert(static_cast<size_t>(kWarps) * kStages * PAGE >= sizeof(float) * kWarps * 8 * kOPad,
                   "ring must hold the merge buffer");
     auto kern = decode_partial_kernel<KB, VB, QJL, SPARSE, kStages>;
@@ -661,7 +602,7 @@ int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TQ_ERR_LAUNCH;
     if (!configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_max)) != cudaSuccess)
             return TQ_ERR_LAUNCH;
         configured[dev] = true;
     }
@@ -774,6 +715,7 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     p.chunk_pages = chunk_pages;
     p.max_chunks = max_chunks;
     p.io_dtype = io_dtype;
+    p.share_tables = (k_bits == v_bits && k_centroids == v_centroids) ? 1 : 0;
 
     const dim3 grid(max_chunks, num_kv_heads * p.ngroups, num_seqs);
     const bool qjl = use_qjl != 0, sparse = sparse_thresh > 0.f;

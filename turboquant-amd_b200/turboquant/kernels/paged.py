@@ -61,12 +61,13 @@ class Codebooks:
         kc, kb = k_codebook if k_codebook is not None else make_codebook(128, fmt.k_bits)
         if v_codebook is not None:
             vc, vb = v_codebook
-        elif fmt.v_bits == fmt.k_bits and k_codebook is not None:
-            vc, vb = kc, kb
+        elif fmt.v_bits == fmt.k_bits:
+            vc, vb = kc, kb          # one tensor for both: the decode kernel then keeps a single lookup table
         else:
             vc, vb = make_codebook(128, fmt.v_bits)
         f = lambda t: t.to(device=dev, dtype=torch.float32).contiguous()
-        self.kc, self.kb, self.vc, self.vb = f(kc), f(kb), f(vc), f(vb)
+        self.kc, self.kb = f(kc), f(kb)
+        self.vc, self.vb = (self.kc, self.kb) if vc is kc else (f(vc), f(vb))
 
 
 def allocate_cache(num_blocks: int, block_size: int, num_kv_heads: int, fmt: CacheFormat, device) -> torch.Tensor:
