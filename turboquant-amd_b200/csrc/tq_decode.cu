@@ -342,6 +342,43 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     uint32_t v_seen = 0, v_skipped = 0;
     uint32_t v_parity = 0;                  // bit s: phase of the V barrier of stage s (sparse mode)
     int j_stop = n_my;
+    float lag_p[4] = {0.f, 0.f, 0.f, 0.f};   // sparse mode: weights of the page whose V part is still in flight
+    float al_lag0 = 1.f, al_lag1 = 1.f;
+    bool lag_do_v = false;
+    int lag_valid = kPageTokens;
+
+    auto wait_v = [&](int j) -> bool {
+        const int s = j % NSTAGE;
+        const bool ok = mbar_wait_bounded(mybar + NSTAGE + s, (v_parity >> s) & 1u);
+        v_parity ^= 1u << s;
+        return ok;
+    };
+    // O += P V for page j (already resident in its ring stage); weights are relative to the running maximum.
+    auto accumulate_v = [&](int j, float w0, float w1, float w2, float w3, int valid_tokens) {
+        const uint8_t* pg = myring + (j % NSTAGE) * PAGE;
+        const bool va = gid < valid_tokens, vb = gid + 8 < valid_tokens;
+        const float2 vn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + VN_OFF + gid * 4));
+        const uint32_t pr0 = pack_half2(va ? w0 * vn.x : 0.f, va ? w1 * vn.x : 0.f);
+        const uint32_t pr1 = pack_half2(vb ? w2 * vn.y : 0.f, vb ? w3 * vn.y : 0.f);
+        const uint32_t t[2] = {movmatrix_trans(pr0), movmatrix_trans(pr1)};
+#pragma unroll
+        for (int o = 0; o < 2; ++o) {
+            const uint32_t pa0 = t[o] & 0xffffu, pa1 = t[o] << 16, pa2 = t[o] >> 16, pa3 = t[o] & 0xffff0000u;
+            uint32_t pw[VB];
+#pragma unroll
+            for (int i = 0; i < VB; ++i)
+                pw[i] = *reinterpret_cast<const uint32_t*>(pg + KPART + ((i * 8 + (4 * o + tig)) * 8 + gid) * 4);
+            uint32_t mv[4];
+            masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t a0 = lut_pair(vlut, mv[u], 0), a1 = lut_pair(vlut, mv[u], 1);
+                const uint32_t b0 = lut_pair(vlut, mv[u], 2), b1 = lut_pair(vlut, mv[u], 3);
+                mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
+                mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
+            }
+        }
+    };
 
     for (int j = 0; j < n_my; ++j) {
         const int s = j % NSTAGE;
@@ -403,12 +440,9 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
             s3 = fmaf(sq[3] + sq2[3], krn.y, s3);
         }
         // only the last page of a sequence can be partly filled
-        bool va = true, vb = true;
         if (valid_tokens < kPageTokens) {
-            va = gid < valid_tokens;
-            vb = gid + 8 < valid_tokens;
-            if (!va) { s0 = -INFINITY; s1 = -INFINITY; }
-            if (!vb) { s2 = -INFINITY; s3 = -INFINITY; }
+            if (gid >= valid_tokens) { s0 = -INFINITY; s1 = -INFINITY; }
+            if (gid + 8 >= valid_tokens) { s2 = -INFINITY; s3 = -INFINITY; }
         }
 
         // ---- online softmax over the 16 tokens (rows live across the 8 gid lanes)
@@ -423,6 +457,8 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         float p0v = ex2(s0 - mn0), p1v = ex2(s1 - mn1), p2v = ex2(s2 - mn0), p3v = ex2(s3 - mn1);
         if (__any_sync(0xffffffffu, grew)) {
             const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
+            al_lag0 = al0;
+            al_lag1 = al1;
             l0 *= al0;
             l1 *= al1;
             // accumulator rows belong to query gid: fetch its factor from the lane that scored it
@@ -448,44 +484,42 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
             ++v_seen;
             if (!do_v) ++v_skipped;
         }
-        if (do_v) {
-            if constexpr (SPARSE) {
-                issue_v(j);
-                const bool ok = mbar_wait_bounded(mybar + NSTAGE + s, (v_parity >> s) & 1u);
-                v_parity ^= 1u << s;
-                if (!ok) {
-                    timed_out = true;
-                    j_stop = j;
-                    break;
+        if constexpr (!SPARSE) {
+            accumulate_v(j, p0v, p1v, p2v, p3v, valid_tokens);
+            __syncwarp();
+            if (j + NSTAGE < n_my) {
+                // slide the window by 16 so that entries j .. j + NSTAGE stay available
+                if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
+                issue_k(j + NSTAGE);
+            }
+        } else {
+            // The V copy of this page is issued now and consumed one iteration later, behind the K work of
+            // the next page.  Weights kept for the lagged page stay relative to the running maximum: they
+            // are rescaled together with the accumulator whenever the maximum grows.
+            if (do_v) issue_v(j);
+            if (j > 0) {
+                if (__any_sync(0xffffffffu, grew)) {
+                    lag_p[0] *= al_lag0; lag_p[1] *= al_lag1; lag_p[2] *= al_lag0; lag_p[3] *= al_lag1;
+                }
+                if (lag_do_v) {
+                    if (!wait_v(j - 1)) { timed_out = true; j_stop = j; break; }
+                    accumulate_v(j - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], kPageTokens);
+                }
+                __syncwarp();
+                if (j - 1 + NSTAGE < n_my) {
+                    if (j - 1 + NSTAGE >= jbase + 32) load_bt(jbase + 16);
+                    issue_k(j - 1 + NSTAGE);
                 }
             }
-            const float2 vn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + VN_OFF + gid * 4));
-            const uint32_t pr0 = pack_half2(va ? p0v * vn.x : 0.f, va ? p1v * vn.x : 0.f);
-            const uint32_t pr1 = pack_half2(vb ? p2v * vn.y : 0.f, vb ? p3v * vn.y : 0.f);
-            const uint32_t t[2] = {movmatrix_trans(pr0), movmatrix_trans(pr1)};
-#pragma unroll
-            for (int o = 0; o < 2; ++o) {
-                const uint32_t pa0 = t[o] & 0xffffu, pa1 = t[o] << 16, pa2 = t[o] >> 16, pa3 = t[o] & 0xffff0000u;
-                uint32_t pw[VB];
-#pragma unroll
-                for (int i = 0; i < VB; ++i)
-                    pw[i] = *reinterpret_cast<const uint32_t*>(pg + KPART + ((i * 8 + (4 * o + tig)) * 8 + gid) * 4);
-                uint32_t mv[4];
-                masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t a0 = lut_pair(vlut, mv[u], 0), a1 = lut_pair(vlut, mv[u], 1);
-                    const uint32_t b0 = lut_pair(vlut, mv[u], 2), b1 = lut_pair(vlut, mv[u], 3);
-                    mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
-                    mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
-                }
-            }
+            lag_p[0] = p0v; lag_p[1] = p1v; lag_p[2] = p2v; lag_p[3] = p3v;
+            lag_do_v = do_v;
+            lag_valid = valid_tokens;
         }
-        __syncwarp();
-        if (j + NSTAGE < n_my) {
-            // slide the window by 16 so that entries j .. j + NSTAGE stay available
-            if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
-            issue_k(j + NSTAGE);
+    }
+    if constexpr (SPARSE) {
+        if (!timed_out && n_my > 0 && lag_do_v) {
+            if (wait_v(n_my - 1)) accumulate_v(n_my - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], lag_valid);
+            else timed_out = true;
         }
     }
     if (timed_out) {
