@@ -669,9 +669,11 @@ using namespace tq;
 
 extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int num_q_heads, int max_pages_per_seq) {
     if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
-    // About 3 CTAs per resident slot (148 SMs x 4 CTAs) keeps the tail of the last wave small; at
-    // least 64 pages per CTA (16 per warp) keeps the per-CTA prologue and merge amortised.  Measured on
-    // batch 64 x 8192 tokens x 8 KV heads: 128..256 pages per chunk is the flat optimum.
+    // About 3 CTAs per resident slot (148 SMs x 4 CTAs) keeps the tail of the last wave small.  Measured
+    // on batch 64 x 8192 tokens x 8 KV heads: 128..256 pages per chunk is the flat optimum.  At least 16
+    // pages per CTA keep the prologue (lookup-table fill, query fragments) amortised for tiny batches; at
+    // most 256 pages per CTA bound the longest CTA when sequence lengths are skewed (the sizes are chosen
+    // from the longest sequence; chunks beyond a shorter sequence's end exit at once).
     const int G = num_q_heads / num_kv_heads;
     const int ngroups = (G + 7) / 8;
     const long long pairs = 1LL * num_seqs * num_kv_heads * ngroups;
@@ -679,7 +681,8 @@ extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int nu
     long long chunks = (target_ctas + pairs - 1) / pairs;
     if (chunks < 1) chunks = 1;
     long long cp = (max_pages_per_seq + chunks - 1) / chunks;
-    if (cp < 64) cp = 64;
+    if (cp > 256) cp = 256;
+    if (cp < 16) cp = 16;
     if (cp > max_pages_per_seq) cp = max_pages_per_seq;
     return static_cast<int>(cp);
 }
