@@ -527,7 +527,11 @@ def main():
                          "pct_of_8TBps": 100 * comp_gbs / 8000.0,
                          "how": "CUDA events around compress_and_scatter of each layer's fp16 K+V (fresh inputs)"},
             "roofline": {"bound": "hbm", "achieved": achieved_rank, "peak": peak, "unit": "GB/s",
-                         "frac": achieved_rank / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved_rank / peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape
+                         # (ncu capture summarised in profiles/decode_partial_turbo3_cfg3.md); other shapes: not captured
+                         "traffic": 505980416 if (args.workload == "cfg3" and world == 1) else None,
+                         "peak_source": peak_src,
                          "kernel": "decode_partial_kernel (+ merge) per layer per GPU",
                          "algorithmic_bytes_per_launch": bytes_layer_rank},
             "clocks": clocks,
