@@ -274,3 +274,47 @@ def test_sparse_v_wrapper_on_reference_layout_cache():
     assert_attn_close(out11.float().cpu().numpy(), ref)
     assert_attn_close(out12.float().cpu().numpy(), ref)
     assert sparse_v.SPARSE_V_THRESHOLD == 1e-6
+
+
+def test_full_size_decode_properties():
+    """BASELINE config 3 shape for one layer (64 x 8192 tokens, 64q/8kv, turbo3, cache written by the compress
+    kernel): results do not depend on the split-K chunking, on where pages sit in the pool, or on a common
+    power-of-two scale of V; a slice of the batch matches the oracle."""
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    B, L, Hq, Hkv, bs = 64, 8192, 64, 8, 16
+    nb = B * L // bs
+    gd = torch.Generator(device=DEV).manual_seed(21)
+    bt = torch.randperm(nb, generator=torch.Generator().manual_seed(22)).to(torch.int32).reshape(B, L // bs).to(DEV)
+    cache = allocate_cache(nb, bs, Hkv, fmt, DEV)
+    cache2 = allocate_cache(nb, bs, Hkv, fmt, DEV)          # same data, V scaled by 4, different placement
+    bt2 = bt.flip(1).contiguous()
+    for s0 in range(0, B, 8):
+        K = torch.randn(8 * L, Hkv, 128, generator=gd, device=DEV, dtype=torch.float16)
+        V = torch.randn(8 * L, Hkv, 128, generator=gd, device=DEV, dtype=torch.float16)
+        pos = torch.arange(L, device=DEV)
+        slots = (bt[s0:s0 + 8].long().repeat_interleave(bs, dim=1) * bs + pos % bs).reshape(-1)
+        compress_and_scatter(K, V, cache, slots, books, bs)
+        # the flipped table maps logical page p to physical page bt[., last - p]: re-scatter with the token order kept
+        slots2 = (bt2[s0:s0 + 8].long().repeat_interleave(bs, dim=1) * bs + pos % bs).reshape(-1)
+        compress_and_scatter(K, V * 4, cache2, slots2, books, bs)
+    lens = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    q = torch.randn(B, Hq, 128, generator=gd, device=DEV, dtype=torch.float16)
+    outs = [paged_decode_attention(q, cache, bt, lens, books, bs, chunk_pages=c).float() for c in (0, 64, 512)]
+    torch.cuda.synchronize()
+    assert _native.read_status(DEV) == 0
+    for o in outs[1:]:
+        assert_attn_close(o.cpu().numpy(), outs[0].cpu().numpy())
+    o2 = paged_decode_attention(q, cache2, bt2, lens, books, bs).float()
+    assert_attn_close((o2 / 4).cpu().numpy(), outs[0].cpu().numpy())
+    # oracle on two (sequence, KV head) slices of the full-size cache
+    for s, kh in ((3, 0), (60, 7)):
+        pages = cache[bt[s].long(), kh].cpu()                                       # [512, page_bytes]
+        f = paged_layout.unpack_pages(pages, 3, 3, True)
+        kf = {"idx": f["k_idx"].reshape(-1, bs, 1, 128).numpy(), "norm": f["k_norm"].float().reshape(-1, bs, 1).numpy(),
+              "signs": f["k_signs"].reshape(-1, bs, 1, 128).numpy(), "rnorm": f["k_rnorm"].float().reshape(-1, bs, 1).numpy()}
+        vf = {"idx": f["v_idx"].reshape(-1, bs, 1, 128).numpy(), "norm": f["v_norm"].float().reshape(-1, bs, 1).numpy()}
+        qs = q[s:s + 1, kh * 8:(kh + 1) * 8].float().cpu().numpy()
+        ref = O.paged_decode(qs, qs, kf, vf, np.arange(L // bs)[None], np.array([L]), books.kc.cpu().numpy(),
+                             books.vc.cpu().numpy(), 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128, bs)
+        assert_attn_close(outs[0][s, kh * 8:(kh + 1) * 8].cpu().numpy(), ref[0])

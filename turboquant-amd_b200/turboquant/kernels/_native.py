@@ -208,7 +208,8 @@ def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc
     ns, Hq, _ = q_rot.shape
     nb, Hkv, row = cache.shape
     sub = block_size // 16
-    # The check MI355X_BLOCKSIZE_FIX asks for: the kernel's idea of the block size must be the cache's.
+    # The kernel's idea of the block size must be the cache's (the mismatch behind the reference's
+    # intermittent Sparse-V fault, docs/MI355X_BLOCKSIZE_FIX.md:18-21 of the reference).
     if block_size % 16 or row != sub * page_bytes(k_bits, v_bits, use_qjl):
         raise ValueError(f"cache row of {row} bytes does not match block_size {block_size} and the format "
                          f"({sub * page_bytes(k_bits, v_bits, use_qjl)} expected)")
