@@ -188,3 +188,27 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_native, "_lib", None)
     with pytest.raises(RuntimeError, match="not found"):
         _native.lib()
+
+
+# ---- weight fusion (turboquant/core/rotation.py:47-140; the reference's tests/test_rotation.py:73-126) ----
+def test_weight_fusion_equals_explicit_rotation():
+    from turboquant.core.rotation import apply_weight_fusion, fuse_rotation_into_o_proj, fuse_rotation_into_qkv_proj
+    nh, nkv, D, hid = 4, 2, 128, 512
+    torch.manual_seed(42)
+    H = make_wht_matrix(D)
+    qkv = torch.randn((nh + 2 * nkv) * D, hid)
+    x = torch.randn(2, hid)
+    out = x @ qkv.T
+    fused = x @ fuse_rotation_into_qkv_proj(qkv.clone(), nh, nkv, D).T
+    for lo, n in ((0, nh), (nh * D, nkv), ((nh + nkv) * D, nkv)):
+        a = out[:, lo:lo + n * D].view(2, n, D) @ H
+        assert (a - fused[:, lo:lo + n * D].view(2, n, D)).abs().max() < 1e-3
+    o_w = torch.randn(hid, nh * D)
+    attn_rot = torch.randn(2, nh, D)
+    want = (attn_rot @ H).reshape(2, -1) @ o_w.T
+    got = attn_rot.reshape(2, -1) @ fuse_rotation_into_o_proj(o_w.clone(), nh, D).T
+    assert torch.nn.functional.cosine_similarity(want.reshape(1, -1), got.reshape(1, -1)).item() > 0.9999
+    sd = {"layers.0.qkv_proj.weight": qkv.clone(), "layers.0.o_proj.weight": o_w.clone(), "other": torch.ones(2)}
+    sd2 = apply_weight_fusion(sd, nh, nkv, D)
+    assert sd2 is sd and torch.equal(sd["other"], torch.ones(2))
+    assert torch.allclose(sd["layers.0.qkv_proj.weight"], fuse_rotation_into_qkv_proj(qkv, nh, nkv, D))
