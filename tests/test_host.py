@@ -151,7 +151,7 @@ def test_host_only_entry_points():
     assert L.tq_version() >= 1
     assert L.tq_page_bytes(5, 3, 1) == -2 and L.tq_page_bytes(3, 1, 0) == -2
     cp = L.tq_decode_auto_chunk_pages(64, 8, 64, 512)
-    assert cp == 128
+    assert cp == 256
     assert L.tq_decode_workspace_bytes(64, 64, 8, 512, cp) == 64 * 8 * ((512 + cp - 1) // cp) * 8 * 130 * 4
     assert L.tq_decode_auto_chunk_pages(1, 8, 32, 1) == 1
     assert L.tq_decode_auto_chunk_pages(64, 1, 8, 512) == 64          # one KV head per GPU: 8 chunks of 64 pages

@@ -670,22 +670,25 @@ using namespace tq;
 extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int num_q_heads, int max_pages_per_seq) {
     if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
     // Sizes come from the longest sequence; chunks beyond a shorter sequence's end exit at once.
-    //  * about 3 CTAs per resident slot (148 SMs x 4 CTAs) keep the tail of the last wave small, but a
-    //    CTA should keep >= 64 pages (16 per warp) so that its prologue (lookup-table fill, query
-    //    fragments, first copies) stays amortised: measured on batch 64 x 8192 tokens, 64-page chunks win
-    //    for 1 or 2 KV heads per GPU, 128..256-page chunks for 8;
-    //  * if that leaves the GPU less than half full (tiny batches), chunks shrink down to 16 pages;
-    //  * at most 256 pages per CTA bound the longest CTA when sequence lengths are skewed;
-    //  * the chunk size is then evened out so that all chunks of the longest sequence are alike.
+    // Measured on batch 64 x 8192 tokens with 1, 2, 4 and 8 KV heads per GPU (chunk sizes 32..512 pages):
+    //  * about 1024 CTAs (1.7 waves of 148 SMs x 4 CTAs) is the flat optimum, with a power-of-two number
+    //    of chunks so that all chunks of a sequence are alike (64-page chunks for 1-2 heads, 128 for 4,
+    //    128..256 for 8); uneven splits such as 57 or 74 pages lose 5-10 %;
+    //  * a CTA keeps >= 64 pages (16 per warp) so that its prologue (lookup-table fill, query fragments,
+    //    first copies) stays amortised, unless that leaves the GPU less than half full (tiny batches):
+    //    then chunks shrink down to 16 pages;
+    //  * at most 256 pages per CTA bound the longest CTA when sequence lengths are skewed.
     const int G = num_q_heads / num_kv_heads;
     const int ngroups = (G + 7) / 8;
     const long long pairs = 1LL * num_seqs * num_kv_heads * ngroups;
     const long long slots = 148LL * 4;
     auto ceil_div = [](long long a, long long b) { return (a + b - 1) / b; };
+    long long chunks = 1;
+    while (pairs * chunks * 2 <= 1024 + pairs * chunks / 2) chunks *= 2;   // power of two nearest to 1024 / pairs
     long long max_big = max_pages_per_seq / 64;
     if (max_big < 1) max_big = 1;
-    long long chunks = ceil_div(3 * slots, pairs);
-    if (chunks > max_big) chunks = max_big;
+    while (chunks > max_big) chunks /= 2;
+    if (chunks < 1) chunks = 1;
     if (pairs * chunks < slots / 2) {
         long long max_small = max_pages_per_seq / 16;
         if (max_small < 1) max_small = 1;
@@ -694,7 +697,6 @@ extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int nu
     }
     long long cp = ceil_div(max_pages_per_seq, chunks);
     if (cp > 256) cp = 256;
-    cp = ceil_div(max_pages_per_seq, ceil_div(max_pages_per_seq, cp));
     return static_cast<int>(cp);
 }
 
