@@ -36,6 +36,11 @@ typedef struct CUstream_st* tq_stream_t; /* same type as cudaStream_t */
 #define TQ_DTYPE_BF16 1
 #define TQ_DTYPE_F32 2
 
+/* Flags that may be OR-ed into the io_dtype argument of tq_decode_paged / tq_decode_paged_static. */
+#define TQ_IO_ROTATE_Q 0x100     /* q_rot is given in ORIGINAL space: the kernel rotates it (q' = q H) while loading;
+                                    q_proj must be NULL */
+#define TQ_IO_DEROTATE_OUT 0x200 /* write out in original space (out H), as the reference's rotate_output does */
+
 /* Bits set by kernels in the optional device-side status word. */
 #define TQ_STATUS_BAD_BLOCK 1 /* a block-table entry was outside [0, num_blocks) and was clamped */
 #define TQ_STATUS_TIMEOUT 2   /* a bounded wait on an async copy ran out */
@@ -97,7 +102,9 @@ int64_t tq_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_head
  * 274-295).
  *
  * out, q_rot, q_proj: [num_seqs, num_q_heads, 128] of io_dtype (fp16 or
- * bf16); q_rot is the query in rotated space, q_proj = S q_rot (pass q_rot,
+ * bf16, optionally OR-ed with TQ_IO_ROTATE_Q / TQ_IO_DEROTATE_OUT to fuse the two
+ * rotations of TurboQuantFP8State.rotate_query / rotate_output,
+ * turboquant/integration/vllm_backend.py:158-176, into this call); q_rot is the query in rotated space, q_proj = S q_rot (pass q_rot,
  * or NULL, when S = I).  score = sm_scale * (k_norm <q_rot, c[k_idx]> +
  * corr_scale * k_rnorm <q_proj, signs>); out = softmax(score) applied to
  * v_norm * c_v[v_idx], in rotated space.  Query head h reads kv head

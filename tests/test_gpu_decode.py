@@ -318,3 +318,28 @@ def test_full_size_decode_properties():
         ref = O.paged_decode(qs, qs, kf, vf, np.arange(L // bs)[None], np.array([L]), books.kc.cpu().numpy(),
                              books.vc.cpu().numpy(), 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128, bs)
         assert_attn_close(outs[0][s, kh * 8:(kh + 1) * 8].cpu().numpy(), ref[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_rotations_match_separate_passes(dtype):
+    """TQ_IO_ROTATE_Q / TQ_IO_DEROTATE_OUT: rotating inside the decode kernels gives what wht_rows before and
+    after the call gives (the fused query is rounded to the io dtype exactly like the separate pass)."""
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    lens = torch.tensor([700, 90, 16, 0], dtype=torch.int32)      # multi-chunk, single-chunk, one page, empty
+    f = random_fields(fmt, 64, 16, 2, 5)
+    cache = paged_layout.pack_cache(f, 16, 3, 3, True).to(DEV)
+    g = torch.Generator().manual_seed(6)
+    bt = torch.stack([torch.randperm(64, generator=g)[:44] for _ in range(4)]).to(torch.int32).to(DEV)
+    q = torch.randn(4, 16, 128, generator=g).to(dtype).to(DEV)
+    q_rot = _native.wht_rows(q)
+    for chunk in (0, 4):
+        sep_rot = paged_decode_attention(q_rot, cache, bt, lens.to(DEV), books, 16, chunk_pages=chunk)
+        fused_q = paged_decode_attention(q, cache, bt, lens.to(DEV), books, 16, chunk_pages=chunk, rotate_q=True)
+        assert torch.equal(fused_q, sep_rot)
+        sep_out = _native.wht_rows(sep_rot)
+        fused = paged_decode_attention(q, cache, bt, lens.to(DEV), books, 16, chunk_pages=chunk, rotate_q=True,
+                                       derotate_out=True)
+        tol = 2e-3 if dtype == torch.float16 else 1.6e-2           # one rounding to the output dtype less than two
+        assert (fused.float() - sep_out.float()).abs().max().item() <= tol
+        assert (fused[3] == 0).all()

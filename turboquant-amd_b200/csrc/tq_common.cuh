@@ -125,4 +125,26 @@ __device__ __forceinline__ void load4(const void* base, int64_t elem_off, int dt
     }
 }
 
+// ---- 128-point WHT over a group of 4 lanes (unnormalised) ---------------------------------------
+__device__ __forceinline__ void fwht128(float (&x)[32], int lane) {
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (!(i & h)) {
+                const float a = x[i], b = x[i + h];
+                x[i] = a + b;
+                x[i + h] = a - b;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1) {
+        const float sgn = (lane & m) ? -1.f : 1.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = fmaf(sgn, x[i], __shfl_xor_sync(0xffffffffu, x[i], m));
+    }
+}
+
+
 }  // namespace tq

@@ -64,6 +64,8 @@ struct DecodeParams {
     int chunk_pages, max_chunks;
     int io_dtype;
     int share_tables;        // K and V use the same codebook: one pair table serves both
+    int rotate_q;            // the query is in original space: rotate it (fast WHT) while loading
+    int derotate_out;        // write the output in original space
 };
 
 // ---------------------------------------------------------------------------------
@@ -127,16 +129,14 @@ __device__ __forceinline__ uint32_t lut_pair(uint32_t lane_base, uint32_t mw, in
 // the constant sum of the query over those dims is subtracted once (accumulator start value).
 // Form 0 yields -sigma, so its query operand is negated.  All query operands carry 1/16 to keep
 // 2^12 * q inside fp16; the factor 16 is folded into the fp32 scale of the residual norm.
-__device__ __forceinline__ void load_qp_frag_signed(const void* q, int64_t row_off, int tig, int io_dtype, bool valid,
-                                                    uint32_t (&f)[16], float& correction) {
-    correction = 0.f;
+// This lane's 32 query values (dims 32 * tig .. 32 * tig + 31 of query row gid) as fp32; zeros when !valid.
+__device__ __forceinline__ void load_q32(const void* q, int64_t row_off, int tig, int io_dtype, bool valid, float (&x)[32]) {
     if (!valid) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = 0u;
+        for (int i = 0; i < 32; ++i) x[i] = 0.f;
         return;
     }
     const uint16_t* base = static_cast<const uint16_t*>(q) + row_off + tig * 32;
-    float x[32];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + i);
@@ -153,6 +153,28 @@ __device__ __forceinline__ void load_qp_frag_signed(const void* q, int64_t row_o
             }
         }
     }
+}
+
+// q' = q H for the query row spread over the 4 lanes of a tig group, rounded to the io dtype exactly as
+// a separate rotation pass writing fp16 / bf16 would.
+__device__ __forceinline__ void rotate_q32(float (&x)[32], int lane, int io_dtype) {
+    fwht128(x, lane);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float v = x[i] * kWhtScale;
+        x[i] = io_dtype == TQ_DTYPE_F16 ? __half2float(__float2half_rn(v)) : __bfloat162float(__float2bfloat16_rn(v));
+    }
+}
+
+__device__ __forceinline__ void q_frag_from(const float (&x)[32], uint32_t (&f)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = pack_half2(x[2 * i], x[2 * i + 1]);
+}
+
+// Query operands of the sign term (see above): per MMA m and slot, half2 of dims (j, j + 16) times the
+// coefficient of the form; `correction` returns this lane's share of the query sum over the one-sided forms.
+__device__ __forceinline__ void qp_frag_signed_from(const float (&x)[32], uint32_t (&f)[16], float& correction) {
+    correction = 0.f;
     const float coef[4] = {-1.f / 16.f, 1.f / 16.f, 16.f, 256.f};   // form 0..3, times the common 1/16
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
@@ -179,32 +201,23 @@ __device__ __forceinline__ void lds_words(const uint8_t* p, uint32_t (&w)[NW]) {
     }
 }
 
-// Load one query row slice (32 values at q[32*tig ..]) scaled, as 16 half2 registers.
-__device__ __forceinline__ void load_q_frag(const void* q, int64_t row_off, int tig, int io_dtype, float scale,
-                                            bool valid, uint32_t (&f)[16]) {
-    if (!valid) {
+// Output de-rotation inside a block: 128 threads hold one value each (thread = dim); returns (v H)[dim].
+// Five butterfly stages by warp shuffle, two through shared memory (buf: 128 floats).
+__device__ __forceinline__ float block_wht128(float v, float* buf, int tid) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = 0u;
-        return;
+    for (int m = 1; m < 32; m <<= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, m);
+        v = (tid & m) ? o - v : v + o;
     }
-    const uint16_t* base = static_cast<const uint16_t*>(q) + row_off + tig * 32;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(base) + i);
-        const uint32_t r[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float lo, hi;
-            if (io_dtype == TQ_DTYPE_F16) {
-                const float2 t = unpack_half2(r[j]);
-                lo = t.x; hi = t.y;
-            } else {
-                lo = __uint_as_float(r[j] << 16);
-                hi = __uint_as_float(r[j] & 0xffff0000u);
-            }
-            f[i * 4 + j] = pack_half2(lo * scale, hi * scale);
-        }
+    for (int m = 32; m < 128; m <<= 1) {
+        buf[tid] = v;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const float o = buf[tid ^ m];
+        v = (tid & m) ? o - v : v + o;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
     }
+    return v * kWhtScale;
 }
 
 template <int KB, int VB, bool QJL, bool SPARSE, int NSTAGE>
@@ -225,6 +238,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     float* sm_o = reinterpret_cast<float*>(ring);                       // reused after the page loop
     __shared__ float sm_m[kWarps][8];
     __shared__ float sm_l[kWarps][8];
+    __shared__ float sm_wht[kHeadDim];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -270,10 +284,14 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     {
         const bool valid = g_in_group < p.G;
         const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
-        load_q_frag(p.q, row, tig, p.io_dtype, 1.f, valid, qf);
+        float xq[32];
+        load_q32(p.q, row, tig, p.io_dtype, valid, xq);
+        if (p.rotate_q) rotate_q32(xq, lane, p.io_dtype);
+        q_frag_from(xq, qf);
         if constexpr (QJL) {
+            if (p.qp) load_q32(p.qp, row, tig, p.io_dtype, valid, xq);   // S q' given separately
             float corr;
-            load_qp_frag_signed(p.qp ? p.qp : p.q, row, tig, p.io_dtype, valid, qpf, corr);
+            qp_frag_signed_from(xq, qpf, corr);
             corr += __shfl_xor_sync(0xffffffffu, corr, 1);
             corr += __shfl_xor_sync(0xffffffffu, corr, 2);      // total over the 128 dims of query gid
             sq_init0 = -__shfl_sync(0xffffffffu, corr, 8 * tig);       // query 2 * tig lives on lanes 8 * tig ..
@@ -580,7 +598,8 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
             l = fmaf(sc, sm_l[w][g], l);
         }
         if (nchunks == 1) {
-            const float r = o / l;
+            float r = o / l;
+            if (p.derotate_out) r = block_wht128(r, sm_wht, dim);
             const int64_t off = (static_cast<int64_t>(seq) * p.Hq + head0 + g) * kHeadDim + dim;
             if (p.io_dtype == TQ_DTYPE_F16)
                 static_cast<__half*>(p.out)[off] = __float2half_rn(r);
@@ -615,7 +634,11 @@ __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const DecodePara
         o = fmaf(sc, p.ws_o[slot * kHeadDim + dim], o);
         l = fmaf(sc, p.ws_ml[slot * 2 + 1], l);
     }
-    const float r = o / l;
+    float r = o / l;
+    if (p.derotate_out) {
+        __shared__ float buf[kHeadDim];
+        r = block_wht128(r, buf, dim);
+    }
     const int64_t off = (static_cast<int64_t>(seq) * p.Hq + head) * kHeadDim + dim;
     if (p.io_dtype == TQ_DTYPE_F16)
         static_cast<__half*>(p.out)[off] = __float2half_rn(r);
@@ -722,7 +745,10 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     if (!out || !q_rot || !cache || !block_tables || !seq_lens || !k_centroids || !v_centroids) return TQ_ERR_ARG;
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0 || num_blocks <= 0) return TQ_ERR_ARG;
     if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
+    const int rotate_q = (io_dtype & TQ_IO_ROTATE_Q) ? 1 : 0, derotate_out = (io_dtype & TQ_IO_DEROTATE_OUT) ? 1 : 0;
+    io_dtype &= 0xff;
     if (io_dtype != TQ_DTYPE_F16 && io_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
+    if (rotate_q && q_proj) return TQ_ERR_ARG;   // S q' cannot be derived from an unrotated query
     if (block_size < kPageTokens || (block_size & (block_size - 1))) return TQ_ERR_UNSUPPORTED;  // 16, 32, 64, ...
     if (k_bits < 2 || k_bits > 4 || v_bits < 2 || v_bits > 4) return TQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(q_rot) | reinterpret_cast<uintptr_t>(out) |
@@ -765,6 +791,8 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     p.chunk_pages = chunk_pages;
     p.max_chunks = max_chunks;
     p.io_dtype = io_dtype;
+    p.rotate_q = rotate_q;
+    p.derotate_out = derotate_out;
     p.share_tables = (k_bits == v_bits && k_centroids == v_centroids) ? 1 : 0;
 
     const dim3 grid(max_chunks, num_kv_heads * p.ngroups, num_seqs);

@@ -7,7 +7,7 @@ TQ_FP4_PA_SO plays in the reference, turboquant/integration/tq_fp4_backend.py:59
 Ops registered (namespace `tq_b200`):
   compress_paged(key, value, cache, slot_mapping, kc, kb, vc, vb, block_size, k_bits, v_bits, use_qjl, prerotated)
   decode_paged(q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale, sparse_thresh,
-               block_size, k_bits, v_bits, use_qjl, chunk_pages) -> out
+               block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags) -> out
   wht_rows(x, scale) -> x @ H * scale
 """
 from __future__ import annotations
@@ -24,6 +24,8 @@ _ERRORS = {-1: "bad argument", -2: "unsupported configuration", -3: "CUDA launch
 STATUS_BAD_BLOCK = 1
 STATUS_TIMEOUT = 2
 STATUS_BAD_SLOT = 4
+IO_ROTATE_Q = 0x100        # q is in original space: rotate it inside the decode kernel
+IO_DEROTATE_OUT = 0x200    # write the decode output in original space
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -193,7 +195,8 @@ def decode_chunk_pages(num_seqs: int, num_kv_heads: int, num_q_heads: int, max_p
 
 
 def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale,
-                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, skip_stats=None) -> None:
+                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, skip_stats=None,
+                       io_flags: int = 0) -> None:
     dev = _require_cuda(out, q_rot, cache, block_tables, seq_lens, kc, vc)
     if q_rot.dim() != 3 or q_rot.shape[-1] != 128 or not q_rot.is_contiguous():
         raise ValueError("q must be contiguous [num_seqs, q_heads, 128]")
@@ -230,7 +233,7 @@ def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc
         chunk_pages = L.tq_decode_auto_chunk_pages(ns, Hkv, Hq, max_pages)
     common_tail = (_ptr(status_word(dev)), _ptr(skip_stats), ns, Hq, Hkv, max_pages, k_bits, v_bits, int(use_qjl),
                    chunk_pages, _stream(dev))
-    head = (_ptr(out), _ptr(q_rot), _ptr(q_proj), _DTYPES[q_rot.dtype], _ptr(cache), nb, block_size,
+    head = (_ptr(out), _ptr(q_rot), _ptr(q_proj), _DTYPES[q_rot.dtype] | int(io_flags), _ptr(cache), nb, block_size,
             _ptr(block_tables), block_tables.stride(0), _ptr(seq_lens), _ptr(kc), _ptr(vc),
             float(sm_scale), float(corr_scale), float(sparse_thresh))
     with torch.cuda.device(dev):
@@ -300,16 +303,16 @@ def _(key, value, cache, slot_mapping, kc, kb, vc, vb, block_size, k_bits, v_bit
 def decode_paged_op(q_rot: torch.Tensor, q_proj: Optional[torch.Tensor], cache: torch.Tensor,
                     block_tables: torch.Tensor, seq_lens: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor,
                     sm_scale: float, corr_scale: float, sparse_thresh: float, block_size: int, k_bits: int,
-                    v_bits: int, use_qjl: bool, chunk_pages: int) -> torch.Tensor:
+                    v_bits: int, use_qjl: bool, chunk_pages: int, io_flags: int = 0) -> torch.Tensor:
     out = torch.empty_like(q_rot)
     _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale,
-                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages)
+                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags=io_flags)
     return out
 
 
 @decode_paged_op.register_fake
 def _(q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale, sparse_thresh, block_size,
-      k_bits, v_bits, use_qjl, chunk_pages):
+      k_bits, v_bits, use_qjl, chunk_pages, io_flags=0):
     return torch.empty_like(q_rot)
 
 

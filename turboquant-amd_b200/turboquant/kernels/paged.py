@@ -109,20 +109,24 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
     if corr_scale is None:
         corr_scale = math.sqrt(math.pi / 2) / 128
     q = q.contiguous()
-    q_rot = _native.wht_rows(q) if rotate_q else q
+    # Both rotations run inside the decode kernels (query rotated while its fragments are loaded, output
+    # de-rotated where it is normalised); only a separate q_proj forces the query rotation to be its own pass.
+    flags = _native.IO_DEROTATE_OUT if derotate_out else 0
+    if rotate_q and q_proj is None:
+        flags |= _native.IO_ROTATE_Q
+        q_in = q
+    else:
+        q_in = _native.wht_rows(q) if rotate_q else q
     if block_tables.dtype != torch.int32:
         block_tables = block_tables.to(torch.int32)
     if seq_lens.dtype != torch.int32:
         seq_lens = seq_lens.to(torch.int32)
     if out is None and skip_stats is None:
-        res = torch.ops.tq_b200.decode_paged(q_rot, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc,
-                                             books.vc, float(sm_scale), float(corr_scale), float(sparse_thresh),
-                                             block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, int(chunk_pages))
-    else:
-        res = out if out is not None else torch.empty_like(q_rot)
-        _native._decode_paged_impl(res, q_rot, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc, books.vc,
-                                   sm_scale, corr_scale, sparse_thresh, block_size, fmt.k_bits, fmt.v_bits,
-                                   fmt.use_qjl, int(chunk_pages), skip_stats=skip_stats)
-    if derotate_out:
-        res = _native.wht_rows(res, out=res)
+        return torch.ops.tq_b200.decode_paged(q_in, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc,
+                                              books.vc, float(sm_scale), float(corr_scale), float(sparse_thresh),
+                                              block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, int(chunk_pages), flags)
+    res = out if out is not None else torch.empty_like(q_in)
+    _native._decode_paged_impl(res, q_in, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc, books.vc,
+                               sm_scale, corr_scale, sparse_thresh, block_size, fmt.k_bits, fmt.v_bits,
+                               fmt.use_qjl, int(chunk_pages), skip_stats=skip_stats, io_flags=flags)
     return res
