@@ -228,3 +228,24 @@ def test_full_size_properties():
     assert (hist - hist.flip(0)).abs().max() < 2e-3 and hist.min() > 0.02
     # checksum of checksums is reproducible run to run
     assert torch.equal(i1.sum(dtype=torch.int64), packed_compress.compress_k(x, H, None, c.to(DEV), b.to(DEV))[0].sum(dtype=torch.int64))
+
+
+def test_compress_paged_no_tokens_and_fp32_input():
+    fmt = CacheFormat.named("turbo2")
+    books = Codebooks(fmt, DEV)
+    cache = allocate_cache(2, 16, 2, fmt, DEV)
+    before = cache.clone()
+    compress_and_scatter(torch.empty(0, 2, 128, device=DEV), torch.empty(0, 2, 128, device=DEV), cache,
+                         torch.empty(0, dtype=torch.int64, device=DEV), books, 16)
+    assert torch.equal(cache, before)
+    g = torch.Generator().manual_seed(3)
+    K = torch.randn(5, 2, 128, generator=g)
+    V = torch.randn(5, 2, 128, generator=g)
+    slots = torch.tensor([31, 0, 7, 16, 8])
+    compress_and_scatter(K.to(DEV), V.to(DEV), cache, slots.to(DEV), books, 16)
+    assert _native.read_status(DEV) == 0
+    f = paged_layout.unpack_cache(cache.cpu(), 16, 2, 2, True)
+    ok = O.polarquant_compress(K.numpy().reshape(-1, 128), books.kc.cpu().numpy(), books.kb.cpu().numpy(), 2, True,
+                               O.make_wht_matrix(128))
+    got = f["k_idx"][slots // 16, slots % 16].numpy().reshape(-1, 128)
+    assert (got != ok["indices"]).mean() <= 1e-4
