@@ -249,3 +249,66 @@ def test_compress_paged_no_tokens_and_fp32_input():
                                O.make_wht_matrix(128))
     got = f["k_idx"][slots // 16, slots % 16].numpy().reshape(-1, 128)
     assert (got != ok["indices"]).mean() <= 1e-4
+
+
+def test_compress_paged_tight_codebook_takes_generic_path():
+    """Boundaries closer than the table's cell width: the kernel falls back to the binary search."""
+    fmt = CacheFormat.named("turbo3")
+    b = torch.tensor([-0.03, -0.02, -0.01, 0.0, 0.01, 0.02, 0.03])
+    c = torch.tensor([-0.05, -0.025, -0.015, -0.005, 0.005, 0.015, 0.025, 0.05])
+    books = Codebooks(fmt, DEV, k_codebook=(c, b), v_codebook=(c, b))
+    T, Hkv, bs = 40, 2, 16
+    g = torch.Generator().manual_seed(21)
+    key = torch.randn(T, Hkv, 128, generator=g).half()
+    val = torch.randn(T, Hkv, 128, generator=g).half()
+    slots = torch.randperm(4 * bs, generator=g)[:T]
+    for prerotated in (False, True):
+        cache = allocate_cache(4, bs, Hkv, fmt, DEV)
+        compress_and_scatter(key.to(DEV), val.to(DEV), cache, slots.to(DEV), books, bs, prerotated=prerotated)
+        assert _native.read_status(DEV) == 0
+        f = paged_layout.unpack_cache(cache.cpu(), bs, 3, 3, True)
+        H = None if prerotated else O.make_wht_matrix(128)
+        ok = O.polarquant_compress(key.float().numpy().reshape(-1, 128), c.numpy(), b.numpy(), 3, True, H)
+        ov = O.polarquant_compress(val.float().numpy().reshape(-1, 128), c.numpy(), b.numpy(), 3, False, H)
+        got_k = f["k_idx"][slots // bs, slots % bs].numpy().reshape(-1, 128)
+        got_v = f["v_idx"][slots // bs, slots % bs].numpy().reshape(-1, 128)
+        got_s = f["k_signs"][slots // bs, slots % bs].numpy().reshape(-1, 128)
+        if prerotated:
+            assert np.array_equal(got_k, ok["indices"]) and np.array_equal(got_v, ov["indices"])
+            assert np.array_equal(got_s, ok["signs"] > 0)
+        else:
+            assert (got_k != ok["indices"]).mean() <= 1e-3 and (got_v != ov["indices"]).mean() <= 1e-3
+
+
+@pytest.mark.parametrize("dtype,prerotated", [(torch.float16, False), (torch.bfloat16, False), (torch.float16, True),
+                                              (torch.float32, False)])
+def test_compress_paged_nonfinite_rows_do_not_disturb_others(dtype, prerotated):
+    """A NaN or an infinity inside one vector only spoils that vector (its norm shows it)."""
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    T, Hkv, bs = 24, 2, 16
+    g = torch.Generator().manual_seed(23)
+    key = torch.randn(T, Hkv, 128, generator=g).to(dtype)
+    val = torch.randn(T, Hkv, 128, generator=g).to(dtype)
+    slots = torch.arange(T, dtype=torch.int64)
+    clean = allocate_cache(2, bs, Hkv, fmt, DEV)
+    compress_and_scatter(key.to(DEV), val.to(DEV), clean, slots.to(DEV), books, bs, prerotated=prerotated)
+    bad_k, bad_v = key.clone(), val.clone()
+    bad_k[3, 1, 17] = float("nan")
+    bad_k[5, 0, 100] = float("inf")
+    bad_v[7, 1, 0] = float("-inf")
+    dirty = allocate_cache(2, bs, Hkv, fmt, DEV)
+    compress_and_scatter(bad_k.to(DEV), bad_v.to(DEV), dirty, slots.to(DEV), books, bs, prerotated=prerotated)
+    torch.cuda.synchronize()
+    assert _native.read_status(DEV) == 0
+    fc = paged_layout.unpack_cache(clean.cpu(), bs, 3, 3, True)
+    fd = paged_layout.unpack_cache(dirty.cpu(), bs, 3, 3, True)
+    keep_k = torch.ones(2, bs, Hkv, dtype=torch.bool)
+    keep_k[0, 3, 1] = keep_k[0, 5, 0] = False
+    keep_v = torch.ones(2, bs, Hkv, dtype=torch.bool)
+    keep_v[0, 7, 1] = False
+    for name, keep in (("k_idx", keep_k), ("k_signs", keep_k), ("k_norm", keep_k), ("k_rnorm", keep_k),
+                       ("v_idx", keep_v), ("v_norm", keep_v)):
+        assert torch.equal(fc[name][keep], fd[name][keep]), name
+    assert not torch.isfinite(fd["k_norm"][0, 3, 1]) and not torch.isfinite(fd["k_norm"][0, 5, 0])
+    assert not torch.isfinite(fd["v_norm"][0, 7, 1])

@@ -236,61 +236,88 @@ struct PagedParams {
     int Hkv, block_size, in_dtype, rotate;
 };
 
-template <int KB, int VB, bool QJL>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) compress_paged_kernel(const PagedParams p) {
-    constexpr int PAGE = page_bytes(KB, VB, QJL ? 1 : 0);
-    constexpr int KPART = k_part_bytes(KB, QJL ? 1 : 0);
-    __shared__ float csm[1 << KB];
-    if (threadIdx.x < (1 << KB)) csm[threadIdx.x] = p.kc[threadIdx.x];
-    __syncthreads();
-    const int lane = threadIdx.x & 31, quarter = lane & 3;
-    const int64_t item = (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2);
-    // Lanes of items past the end still take part in the shuffles (on zeros) and store nothing.
-    bool live = item < p.n_items;
-    int64_t tok = 0;
-    int head = 0, t = 0;
-    uint8_t* page = nullptr;
-    if (live) {
-        tok = item / p.Hkv;
-        head = static_cast<int>(item - tok * p.Hkv);
-        int64_t slot = p.slot_mapping[tok];
+// Where one (token, head) item goes in the paged cache; live = false when the item is past the end or its
+// slot is out of range (then nothing is stored; a bad slot also raises the status bit).
+struct ItemPlace {
+    int64_t tok;
+    int head, t;
+    uint8_t* page;
+    bool live;
+};
+
+template <int PAGE>
+__device__ __forceinline__ ItemPlace place_item(const PagedParams& p, int64_t item, int quarter) {
+    ItemPlace w;
+    w.tok = 0; w.head = 0; w.t = 0; w.page = nullptr;
+    w.live = item < p.n_items;
+    if (w.live) {
+        if (p.n_items <= 0x7fffffff) {   // uniform over the grid: 32-bit division is several times cheaper
+            const uint32_t tk = static_cast<uint32_t>(item) / static_cast<uint32_t>(p.Hkv);
+            w.tok = tk;
+            w.head = static_cast<int>(static_cast<uint32_t>(item) - tk * static_cast<uint32_t>(p.Hkv));
+        } else {
+            w.tok = item / p.Hkv;
+            w.head = static_cast<int>(item - w.tok * p.Hkv);
+        }
+        int64_t slot = p.slot_mapping[w.tok];
         if (slot < 0) slot = 0;   // the reference clamps padding slots to 0
         if (slot >= p.num_slots) {
             if (quarter == 0 && p.status) atomicOr(p.status, TQ_STATUS_BAD_SLOT);
-            live = false;
+            w.live = false;
         } else {
-            const int64_t blk = slot / p.block_size;
+            int64_t blk;
+            if (p.num_slots <= 0x7fffffff) blk = static_cast<uint32_t>(slot) / static_cast<uint32_t>(p.block_size);
+            else blk = slot / p.block_size;
             const int off = static_cast<int>(slot - blk * p.block_size);
             const int spb = p.block_size / kPageTokens;
-            page = p.cache + ((blk * p.Hkv + head) * spb + off / kPageTokens) * PAGE;
-            t = off % kPageTokens;
+            w.page = p.cache + ((blk * p.Hkv + w.head) * spb + off / kPageTokens) * PAGE;
+            w.t = off % kPageTokens;
         }
     }
+    return w;
+}
+
+// Generic path for one group of 8 items per warp: binary-search bucketize over arbitrary sorted boundaries.
+// Lanes of items past the end still take part in the shuffles (on zeros) and store nothing.
+template <int KB, int VB, bool QJL>
+__device__ __noinline__ void compress_items_generic(const PagedParams& p, int64_t item, int lane, const float* csm) {
+    constexpr int PAGE = page_bytes(KB, VB, QJL ? 1 : 0);
+    constexpr int KPART = k_part_bytes(KB, QJL ? 1 : 0);
+    const int quarter = lane & 3;
+    const ItemPlace w = place_item<PAGE>(p, item, quarter);
     float x[32];
     Quarter q;
     {
         Boundaries<KB> kbd;
         kbd.load(p.kb);
-        if (live) load32(p.key, tok * p.ks_t + head * p.ks_h + 32 * quarter, p.in_dtype, x);
+        if (w.live) load32(p.key, w.tok * p.ks_t + w.head * p.ks_h + 32 * quarter, p.in_dtype, x);
         else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) x[i] = 0.f;
         }
         quantize_quarter<KB, QJL>(x, p.rotate != 0, lane, kbd, csm, q);
-        if (live) store_k_paged<KB, QJL>(page, t, quarter, q);
+        if (w.live) store_k_paged<KB, QJL>(w.page, w.t, quarter, q);
     }
     {
         Boundaries<VB> vbd;
         vbd.load(p.vb);
-        if (live) load32(p.value, tok * p.vs_t + head * p.vs_h + 32 * quarter, p.in_dtype, x);
+        if (w.live) load32(p.value, w.tok * p.vs_t + w.head * p.vs_h + 32 * quarter, p.in_dtype, x);
         else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) x[i] = 0.f;
         }
         quantize_quarter<VB, false>(x, p.rotate != 0, lane, vbd, nullptr, q);
-        if (live) store_v_paged<VB>(page + KPART, t, quarter, q);
+        if (w.live) store_v_paged<VB>(w.page + KPART, w.t, quarter, q);
     }
 }
+
+}  // namespace
+}  // namespace tq
+
+#include "tq_compress_fast.cuh"
+
+namespace tq {
+namespace {
 
 // ---- contiguous outputs ---------------------------------------------------------------------------
 enum class OutMode { kPackedK, kPackedV, kUnpacked };
@@ -409,10 +436,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compress_contig_kernel(cons
 
 template <int KB, int VB>
 int launch_paged(const PagedParams& p, bool qjl, cudaStream_t st) {
-    const unsigned grid = static_cast<unsigned>((p.n_items + kItemsPerCta - 1) / kItemsPerCta);
-    if (qjl) compress_paged_kernel<KB, VB, true><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    else compress_paged_kernel<KB, VB, false><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    return qjl ? launch_paged_fast<KB, VB, true>(p, st) : launch_paged_fast<KB, VB, false>(p, st);
 }
 
 template <int KB>
