@@ -245,20 +245,36 @@ struct ItemPlace {
     bool live;
 };
 
-template <int PAGE>
-__device__ __forceinline__ ItemPlace place_item(const PagedParams& p, int64_t item, int quarter) {
-    ItemPlace w;
-    w.tok = 0; w.head = 0; w.t = 0; w.page = nullptr;
-    w.live = item < p.n_items;
-    if (w.live) {
+// Which token and KV head an item is; live = false past the end.
+struct ItemId {
+    int64_t tok;
+    int head;
+    bool live;
+};
+
+__device__ __forceinline__ ItemId identify_item(const PagedParams& p, int64_t item) {
+    ItemId id;
+    id.tok = 0; id.head = 0;
+    id.live = item < p.n_items;
+    if (id.live) {
         if (p.n_items <= 0x7fffffff) {   // uniform over the grid: 32-bit division is several times cheaper
             const uint32_t tk = static_cast<uint32_t>(item) / static_cast<uint32_t>(p.Hkv);
-            w.tok = tk;
-            w.head = static_cast<int>(static_cast<uint32_t>(item) - tk * static_cast<uint32_t>(p.Hkv));
+            id.tok = tk;
+            id.head = static_cast<int>(static_cast<uint32_t>(item) - tk * static_cast<uint32_t>(p.Hkv));
         } else {
-            w.tok = item / p.Hkv;
-            w.head = static_cast<int>(item - w.tok * p.Hkv);
+            id.tok = item / p.Hkv;
+            id.head = static_cast<int>(item - id.tok * p.Hkv);
         }
+    }
+    return id;
+}
+
+template <int PAGE>
+__device__ __forceinline__ ItemPlace place_item(const PagedParams& p, const ItemId& id, int quarter) {
+    ItemPlace w;
+    w.tok = id.tok; w.head = id.head; w.t = 0; w.page = nullptr;
+    w.live = id.live;
+    if (w.live) {
         int64_t slot = p.slot_mapping[w.tok];
         if (slot < 0) slot = 0;   // the reference clamps padding slots to 0
         if (slot >= p.num_slots) {
@@ -275,6 +291,11 @@ __device__ __forceinline__ ItemPlace place_item(const PagedParams& p, int64_t it
         }
     }
     return w;
+}
+
+template <int PAGE>
+__device__ __forceinline__ ItemPlace place_item(const PagedParams& p, int64_t item, int quarter) {
+    return place_item<PAGE>(p, identify_item(p, item), quarter);
 }
 
 // Generic path for one group of 8 items per warp: binary-search bucketize over arbitrary sorted boundaries.

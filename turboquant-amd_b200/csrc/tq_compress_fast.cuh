@@ -606,25 +606,27 @@ __global__ void __launch_bounds__(kFastWarps * 32, TQ_CMP_MINBLOCKS) compress_pa
         uint4* vbuf = kbuf + 128;
         const uint32_t krow = smem_u32(kbuf + lane), vrow = smem_u32(vbuf + lane);
         const WhtFragments hf = make_wht_fragments(lane, bf16);
+        // Only the identity (token, head) of the next group's item is carried across the loop body; where the
+        // current item goes in the cache is looked up when its turn comes.
         int64_t grp = blockIdx.x;
-        ItemPlace w = place_item<PAGE>(p, grp * kFastItemsPerCta + item0, quarter);
-        stage_row(kbuf, lane, p.key, w.tok * p.ks_t + w.head * p.ks_h + 32 * quarter, w.live);
-        stage_row(vbuf, lane, p.value, w.tok * p.vs_t + w.head * p.vs_h + 32 * quarter, w.live);
+        ItemId id = identify_item(p, grp * kFastItemsPerCta + item0);
+        stage_row(kbuf, lane, p.key, id.tok * p.ks_t + id.head * p.ks_h + 32 * quarter, id.live);
+        stage_row(vbuf, lane, p.value, id.tok * p.vs_t + id.head * p.vs_h + 32 * quarter, id.live);
         while (grp < n_groups) {
+            const ItemPlace w = place_item<PAGE>(p, id, quarter);
             grp += gridDim.x;
-            ItemPlace wn = {0, 0, 0, nullptr, false};
-            if (grp < n_groups) wn = place_item<PAGE>(p, grp * kFastItemsPerCta + item0, quarter);
+            id.live = false;
+            if (grp < n_groups) id = identify_item(p, grp * kFastItemsPerCta + item0);
             wait_staged();
             compress_row_mma<KB, QJL, false>(krow, w.live, lane, bf16, hf, ktab, q, [&] {
-                stage_row(kbuf, lane, p.key, wn.tok * p.ks_t + wn.head * p.ks_h + 32 * quarter, wn.live);
+                stage_row(kbuf, lane, p.key, id.tok * p.ks_t + id.head * p.ks_h + 32 * quarter, id.live);
             });
             if (w.live) store_k_fast<KB, QJL>(w.page, w.t, quarter, q);
             wait_staged();
             compress_row_mma<VB, false, true>(vrow, w.live, lane, bf16, hf, vtab, q, [&] {
-                stage_row(vbuf, lane, p.value, wn.tok * p.vs_t + wn.head * p.vs_h + 32 * quarter, wn.live);
+                stage_row(vbuf, lane, p.value, id.tok * p.vs_t + id.head * p.vs_h + 32 * quarter, id.live);
             });
             if (w.live) store_v_fast<VB>(w.page + KPART, w.t, quarter, q);
-            w = wn;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
