@@ -187,17 +187,28 @@ __device__ __forceinline__ void qp_frag_signed_from(const float (&x)[32], uint32
     }
 }
 
-template <int NW>
-__device__ __forceinline__ void lds_words(const uint8_t* p, uint32_t (&w)[NW]) {
+// Shared-memory loads by 32-bit shared address + compile-time offset (one add per page and access pattern instead
+// of 64-bit generic pointer arithmetic per load).
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+
+template <int NW, int OFF>
+__device__ __forceinline__ void lds_words(uint32_t addr, uint32_t (&w)[NW]) {
     if constexpr (NW == 4) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
-        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr), "n"(OFF));
     } else if constexpr (NW == 2) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
-        w[0] = v.x; w[1] = v.y;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr), "n"(OFF));
     } else {
-#pragma unroll
-        for (int i = 0; i < NW; ++i) w[i] = *reinterpret_cast<const uint32_t*>(p + 4 * i);
+        w[0] = lds_u32<OFF>(addr);
+        if constexpr (NW > 1) w[1] = lds_u32<OFF + 4>(addr);
+        if constexpr (NW > 2) w[2] = lds_u32<OFF + 8>(addr);
+        if constexpr (NW > 3) w[3] = lds_u32<OFF + 12>(addr);
+        if constexpr (NW > 4) w[4] = lds_u32<OFF + 16>(addr);
+        static_assert(NW <= 5, "record has at most 4 index words and a sign word");
     }
 }
 
@@ -279,6 +290,10 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
     __syncthreads();
     const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
+    // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
+    const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
+    const uint32_t ring_n = smem_u32(myring) + gid * 4;
+    const uint32_t ring_v = smem_u32(myring) + (tig * 8 + gid) * 4;
     uint32_t qf[16], qpf[QJL ? 16 : 1];
     float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
     {
@@ -373,19 +388,21 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     };
     // O += P V for page j (already resident in its ring stage); weights are relative to the running maximum.
     auto accumulate_v = [&](int j, float w0, float w1, float w2, float w3, int valid_tokens) {
-        const uint8_t* pg = myring + (j % NSTAGE) * PAGE;
+        const uint32_t stage = (j % NSTAGE) * PAGE;
         const bool va = gid < valid_tokens, vb = gid + 8 < valid_tokens;
-        const float2 vn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + VN_OFF + gid * 4));
+        const float2 vn = unpack_half2(lds_u32<VN_OFF>(ring_n + stage));
+        const uint32_t vaddr = ring_v + stage;
         const uint32_t pr0 = pack_half2(va ? w0 * vn.x : 0.f, va ? w1 * vn.x : 0.f);
         const uint32_t pr1 = pack_half2(vb ? w2 * vn.y : 0.f, vb ? w3 * vn.y : 0.f);
         const uint32_t t[2] = {movmatrix_trans(pr0), movmatrix_trans(pr1)};
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
+            const uint32_t vo = vaddr + o * 128;
             const uint32_t pa0 = t[o] & 0xffffu, pa1 = t[o] << 16, pa2 = t[o] >> 16, pa3 = t[o] & 0xffff0000u;
             uint32_t pw[VB];
 #pragma unroll
             for (int i = 0; i < VB; ++i)
-                pw[i] = *reinterpret_cast<const uint32_t*>(pg + KPART + ((i * 8 + (4 * o + tig)) * 8 + gid) * 4);
+                pw[i] = i == 0 ? lds_u32<KPART>(vo) : (i == 1 ? lds_u32<KPART + 256>(vo) : (i == 2 ? lds_u32<KPART + 512>(vo) : lds_u32<KPART + 768>(vo)));
             uint32_t mv[4];
             masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
 #pragma unroll
@@ -401,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     for (int j = 0; j < n_my; ++j) {
         const int s = j % NSTAGE;
         const uint32_t parity = (j / NSTAGE) & 1;
-        const uint8_t* pg = myring + s * PAGE;
+        const uint32_t stage = s * PAGE;
         if (!mbar_wait_bounded(mybar + s, parity)) {
             timed_out = true;
             j_stop = j;
@@ -411,8 +428,8 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 
         // ---- K: dequantise two token rows (gid, gid + 8) and score them against 8 queries
         uint32_t wa[NWK], wb[NWK];
-        lds_words<NWK>(pg + lane * (NWK * 4), wa);
-        lds_words<NWK>(pg + (lane + 32) * (NWK * 4), wb);
+        lds_words<NWK, 0>(ring_k + stage, wa);
+        lds_words<NWK, 32 * NWK * 4>(ring_k + stage, wb);
         uint32_t mwa[4], mwb[4];
         {
             uint32_t ia[KB], ib[KB];
@@ -444,12 +461,12 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         }
         // The softmax scale (and log2 e) is applied to the fp32 norms, not to the fp16 query, so the
         // query fragments are the caller's fp16 values exactly.
-        float2 kn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KN_OFF + gid * 4));
+        float2 kn = unpack_half2(lds_u32<KN_OFF>(ring_n + stage));
         kn.x *= p.qscale;
         kn.y *= p.qscale;
         float s0 = sm[0] * kn.x, s1 = sm[1] * kn.x, s2 = sm[2] * kn.y, s3 = sm[3] * kn.y;
         if constexpr (QJL) {
-            float2 krn = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + KRN_OFF + gid * 4));
+            float2 krn = unpack_half2(lds_u32<KRN_OFF>(ring_n + stage));
             krn.x *= p.qpscale;
             krn.y *= p.qpscale;
             s0 = fmaf(sq[0] + sq2[0], krn.x, s0);
