@@ -321,7 +321,6 @@ def time_e2e_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     o_dev = [torch.empty_like(q_dev[0]) for _ in range(2)]
     last = (wl.lens - 1).long()
     slots = (wl.block_tables.cpu()[torch.arange(wl.batch), (last // 16)].long() * 16 + last % 16).to(dev)
-    main = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     in_ready = [torch.cuda.Event() for _ in range(2)]
     in_free = [torch.cuda.Event() for _ in range(2)]
@@ -329,6 +328,7 @@ def time_e2e_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     out_free = [torch.cuda.Event() for _ in range(2)]
 
     def step():
+        main = torch.cuda.current_stream(dev)
         s_in.wait_stream(main)
         s_out.wait_stream(main)
         for layer in range(wl.layers):
@@ -339,11 +339,12 @@ def time_e2e_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
                 q_dev[b].copy_(q_host[layer], non_blocking=True)
                 k_dev[b].copy_(k_host[layer], non_blocking=True)
                 v_dev[b].copy_(v_host[layer], non_blocking=True)
+                # the new token is compressed into this layer's cache behind the previous layer's attention
+                compress_and_scatter(k_dev[b], v_dev[b], wl.caches[layer], slots, wl.books, wl.block_size)
                 in_ready[b].record(s_in)
             main.wait_event(in_ready[b])
             if layer >= 2:
                 main.wait_event(out_free[b])
-            compress_and_scatter(k_dev[b], v_dev[b], wl.caches[layer], slots, wl.books, wl.block_size)
             paged_decode_attention(q_dev[b], wl.caches[layer], wl.block_tables, wl.seq_lens, wl.books, wl.block_size,
                                    sparse_thresh=wl.sparse, rotate_q=True, derotate_out=True, out=o_dev[b])
             in_free[b].record(main)
@@ -352,22 +353,36 @@ def time_e2e_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
                 s_out.wait_event(out_ready[b])
                 out_host[layer].copy_(o_dev[b], non_blocking=True)
                 out_free[b].record(s_out)
+        main.wait_stream(s_in)
         main.wait_stream(s_out)
 
+    step()                                         # eager once: sizes the cached workspaces
+    torch.cuda.synchronize()
+    # The whole step - copies on their streams included - is captured once and replayed, as a serving engine
+    # replays its decode step: the pinned host buffers are read and written again by every replay.
+    run, how = step, "eager launches"
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run, how = graph.replay, "one CUDA graph per step"
+    except Exception as exc:                        # capture not possible here: time the eager step
+        print(f"bench: e2e step not captured ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+        torch.cuda.synchronize()
     for _ in range(warmup):
-        step()
+        run()
     torch.cuda.synchronize()
     dist_barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        step()
+        run()
     e1.record()
     torch.cuda.synchronize()
     dist_barrier()
     h2d = wl.layers * (q_host[0].numel() + 2 * k_host[0].numel()) * 2
     d2h = wl.layers * out_host[0].numel() * 2
-    return e0.elapsed_time(e1), h2d, d2h
+    return e0.elapsed_time(e1), h2d, d2h, how
 
 
 def cpu_oracle_sample(fmt_name: str, budget_s: float, threads: int):
@@ -504,8 +519,9 @@ def main():
     ms, skip, outs = time_device_steps(wl, args.steps, args.warmup, barrier)
     clocks = sampler.stop()
     e2e_ms = h2d = d2h = None
+    e2e_how = ""
     if not args.no_e2e:
-        e2e_ms, h2d, d2h = time_e2e_steps(wl, args.steps, args.warmup, barrier)
+        e2e_ms, h2d, d2h, e2e_how = time_e2e_steps(wl, args.steps, args.warmup, barrier)
 
     gather_us = None
     if use_dist:
@@ -570,7 +586,8 @@ def main():
                            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                            "us_per_layer": e2e_sec_layer * 1e6,
                            "what": "pinned-host q + new-token K/V -> H2D, compress+scatter, rotate q, decode, "
-                                   "de-rotate, D2H of the output, every layer; copies double-buffered on their own streams"}
+                                   "de-rotate, D2H of the output, every layer; copies double-buffered on their own "
+                                   "streams; launched as " + e2e_how}
         if gather_us is not None:
             line["output_all_gather_us"] = gather_us
         if not args.no_cpu_baseline and world == 1:
