@@ -285,35 +285,6 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     }
     __syncwarp();
 
-    // ---- per-warp constants: codebooks and query fragments --------------------------
-    fill_pair_lut<KB>(tabk, p.kc, warp, lane);
-    if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
-    __syncthreads();
-    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
-    // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
-    const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
-    const uint32_t ring_n = smem_u32(myring) + gid * 4;
-    const uint32_t ring_v = smem_u32(myring) + (tig * 8 + gid) * 4;
-    uint32_t qf[16], qpf[QJL ? 16 : 1];
-    float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
-    {
-        const bool valid = g_in_group < p.G;
-        const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
-        float xq[32];
-        load_q32(p.q, row, tig, p.io_dtype, valid, xq);
-        if (p.rotate_q) rotate_q32(xq, lane, p.io_dtype);
-        q_frag_from(xq, qf);
-        if constexpr (QJL) {
-            if (p.qp) load_q32(p.qp, row, tig, p.io_dtype, valid, xq);   // S q' given separately
-            float corr;
-            qp_frag_signed_from(xq, qpf, corr);
-            corr += __shfl_xor_sync(0xffffffffu, corr, 1);
-            corr += __shfl_xor_sync(0xffffffffu, corr, 2);      // total over the 128 dims of query gid
-            sq_init0 = -__shfl_sync(0xffffffffu, corr, 8 * tig);       // query 2 * tig lives on lanes 8 * tig ..
-            sq_init1 = -__shfl_sync(0xffffffffu, corr, 8 * tig + 4);   // query 2 * tig + 1
-        }
-    }
-
     // ---- block-table window: lane l holds the entry of this warp's page jbase + l ---
     const int32_t* bt = p.block_tables + static_cast<int64_t>(seq) * p.bt_stride;
     int jbase = 0;
@@ -358,10 +329,41 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         }
     };
 
+    // The first pages are requested before anything else is set up: their HBM latency hides behind the
+    // table fill and the query fragments.
     if (n_my > 0) load_bt(0);
 #pragma unroll
     for (int j = 0; j < NSTAGE; ++j)
         if (j < n_my) issue_k(j);
+
+    // ---- per-warp constants: codebooks and query fragments --------------------------
+    fill_pair_lut<KB>(tabk, p.kc, warp, lane);
+    if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
+    __syncthreads();
+    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
+    // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
+    const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
+    const uint32_t ring_n = smem_u32(myring) + gid * 4;
+    const uint32_t ring_v = smem_u32(myring) + (tig * 8 + gid) * 4;
+    uint32_t qf[16], qpf[QJL ? 16 : 1];
+    float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
+    {
+        const bool valid = g_in_group < p.G;
+        const int64_t row = (static_cast<int64_t>(seq) * p.Hq + head0 + gid) * kHeadDim;
+        float xq[32];
+        load_q32(p.q, row, tig, p.io_dtype, valid, xq);
+        if (p.rotate_q) rotate_q32(xq, lane, p.io_dtype);
+        q_frag_from(xq, qf);
+        if constexpr (QJL) {
+            if (p.qp) load_q32(p.qp, row, tig, p.io_dtype, valid, xq);   // S q' given separately
+            float corr;
+            qp_frag_signed_from(xq, qpf, corr);
+            corr += __shfl_xor_sync(0xffffffffu, corr, 1);
+            corr += __shfl_xor_sync(0xffffffffu, corr, 2);      // total over the 128 dims of query gid
+            sq_init0 = -__shfl_sync(0xffffffffu, corr, 8 * tig);       // query 2 * tig lives on lanes 8 * tig ..
+            sq_init1 = -__shfl_sync(0xffffffffu, corr, 8 * tig + 4);   // query 2 * tig + 1
+        }
+    }
 
     // ---- online-softmax state ---------------------------------------------------------
     float m0 = -INFINITY, m1 = -INFINITY;   // running max for queries 2*tig, 2*tig+1 (log2 domain)
