@@ -466,7 +466,12 @@ def run_reference_arm(args, rank: int):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * statistics.mean(v[2] for v in vals), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {w['desc']} (bounded CPU sample)"},
+            # the same workload as the GPU arm (its config keys); what one CPU step covers is in cpu_baseline.sample
+            "config": {"workload": f"{args.workload}: {w['desc']}", "format": w["fmt"],
+                       "layers": args.layers or w["layers"], "block_size": 16,
+                       "parallelism": f"kv-head sharding x{args.gpus}",
+                       "l2": "host cores: bounded sample of the workload per step, no GPU",
+                       "tolerance": "|diff| <= 2e-3 + 1e-2 |ref| vs fp32 oracle (tests/test_gpu_decode.py)"},
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample,
                              "compress_vectors_per_s": statistics.mean(v[3] for v in vals)},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
