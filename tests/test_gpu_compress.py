@@ -312,3 +312,21 @@ def test_compress_paged_nonfinite_rows_do_not_disturb_others(dtype, prerotated):
         assert torch.equal(fc[name][keep], fd[name][keep]), name
     assert not torch.isfinite(fd["k_norm"][0, 3, 1]) and not torch.isfinite(fd["k_norm"][0, 5, 0])
     assert not torch.isfinite(fd["v_norm"][0, 7, 1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_compress_paged_strided_rows_match_contiguous(dtype):
+    """K and V given as strided views of one fused QKV buffer produce the same cache bytes as contiguous copies."""
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    T, Hkv, bs = 70, 3, 16
+    g = torch.Generator().manual_seed(29)
+    qkv = torch.randn(T, 5 * Hkv, 128, generator=g).to(dtype).to(DEV)
+    key, val = qkv[:, 2 * Hkv:3 * Hkv], qkv[:, 4 * Hkv:]
+    slots = torch.randperm(6 * bs, generator=g)[:T].to(DEV)
+    a = allocate_cache(6, bs, Hkv, fmt, DEV)
+    b = allocate_cache(6, bs, Hkv, fmt, DEV)
+    compress_and_scatter(key, val, a, slots, books, bs)
+    compress_and_scatter(key.contiguous(), val.contiguous(), b, slots, books, bs)
+    assert _native.read_status(DEV) == 0
+    assert torch.equal(a, b)
