@@ -73,8 +73,16 @@ int tq_page_bytes(int k_bits, int v_bits, int use_qjl);
  * 16-byte aligned.  slot_mapping: int64 [n_tokens]; negative slots are
  * clamped to 0 as the reference does (vllm_backend.py:224); slots beyond the
  * cache are skipped and flagged in *status.  centroids: fp32 [2^bits],
- * boundaries: fp32 [2^bits - 1] on the device.  status: optional device
- * int32, OR-ed with TQ_STATUS_* bits; may be NULL. */
+ * boundaries: fp32 [2^bits - 1], ascending, on the device.  status: optional
+ * device int32, OR-ed with TQ_STATUS_* bits; may be NULL.
+ *
+ * The fast path (tensor-core rotation, table-driven bucketize) needs
+ * neighbouring boundaries to be more than 1/64 apart - true of the Lloyd-Max
+ * codebooks for 128 dims at 2, 3 and 4 bits; other codebooks are handled by a
+ * slower generic path with the same results.  A vector that contains a NaN or
+ * an infinity gets the indices of a zero vector and a non-finite norm.  The
+ * first call on a device sets a function attribute (shared-memory size) and
+ * should be made before any stream capture. */
 int tq_compress_paged(const void* key, const void* value, int in_dtype,
                       int64_t k_stride_token, int64_t k_stride_head,
                       int64_t v_stride_token, int64_t v_stride_head,
