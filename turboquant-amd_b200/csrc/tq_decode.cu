@@ -34,11 +34,45 @@ namespace {
 #ifndef TQ_DEC_MINBLOCKS
 #define TQ_DEC_MINBLOCKS 4
 #endif
+#ifndef TQ_DEC_PDL
+#define TQ_DEC_PDL 1
+#endif
 constexpr int kWarps = TQ_DEC_WARPS;
 constexpr int kThreads = kWarps * 32;
 constexpr int kOPad = 132;  // row stride of the merge buffer (floats)
 constexpr int kStages = TQ_DEC_STAGES;  // pages in flight per warp
 constexpr int kBarBytes = kWarps * 2 * kStages * 8;  // mbarriers at the start of dynamic shared memory
+
+// Programmatic dependent launch: the partial and merge kernels of consecutive calls are launched with the
+// stream-serialization attribute, so a kernel's CTAs are scheduled while the previous kernel drains.  Each kernel
+// lets its successor go at once and waits for its predecessor's results before it reads or writes anything; both
+// instructions do nothing in a kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_release_and_wait() {
+#if TQ_DEC_PDL
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+
+template <typename Kernel, typename... Args>
+cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+#if TQ_DEC_PDL
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+#else
+    kernel<<<grid, block, smem, stream>>>(args...);
+    return cudaGetLastError();
+#endif
+}
 
 struct DecodeParams {
     void* out;
@@ -251,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     __shared__ float sm_l[kWarps][8];
     __shared__ float sm_wht[kHeadDim];
 
+    pdl_release_and_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int chunk = blockIdx.x;
@@ -336,15 +371,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     for (int j = 0; j < NSTAGE; ++j)
         if (j < n_my) issue_k(j);
 
-    // ---- per-warp constants: codebooks and query fragments --------------------------
-    fill_pair_lut<KB>(tabk, p.kc, warp, lane);
-    if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
-    __syncthreads();
-    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
-    // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
-    const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
-    const uint32_t ring_n = smem_u32(myring) + gid * 4;
-    const uint32_t ring_v = smem_u32(myring) + (tig * 8 + gid) * 4;
+    // ---- query fragments (their loads are in flight together with the first pages and the table fill) -----
     uint32_t qf[16], qpf[QJL ? 16 : 1];
     float sq_init0 = 0.f, sq_init1 = 0.f;   // minus the query sums of the one-sided sign forms
     {
@@ -365,6 +392,15 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         }
     }
 
+    // ---- per-CTA constants: pair tables of the codebooks ----------------------------------------------
+    fill_pair_lut<KB>(tabk, p.kc, warp, lane);
+    if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
+    __syncthreads();
+    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
+    // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
+    const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
+    const uint32_t ring_n = smem_u32(myring) + gid * 4;
+    const uint32_t ring_v = smem_u32(myring) + (tig * 8 + gid) * 4;
     // ---- online-softmax state ---------------------------------------------------------
     float m0 = -INFINITY, m1 = -INFINITY;   // running max for queries 2*tig, 2*tig+1 (log2 domain)
     float l0 = 0.f, l1 = 0.f;               // this lane's share of the denominators
@@ -636,6 +672,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 }
 
 __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const DecodeParams p) {
+    pdl_release_and_wait();
     const int head = blockIdx.x, seq = blockIdx.y, dim = threadIdx.x;
     const int L = p.seq_lens[seq];
     const int npages = (L + kPageTokens - 1) / kPageTokens;
@@ -682,8 +719,7 @@ int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
             return TQ_ERR_LAUNCH;
         configured[dev] = true;
     }
-    kern<<<grid, kThreads, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    return launch_chained(kern, grid, dim3(kThreads), smem, stream, p) == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
 template <int KB, int VB>
@@ -828,8 +864,8 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     }
     if (rc != TQ_OK) return rc;
     if (max_chunks > 1) {
-        decode_merge_kernel<<<dim3(num_q_heads, num_seqs), kHeadDim, 0, st>>>(p);
-        if (cudaGetLastError() != cudaSuccess) return TQ_ERR_LAUNCH;
+        if (launch_chained(decode_merge_kernel, dim3(num_q_heads, num_seqs), dim3(kHeadDim), 0, st, p) != cudaSuccess)
+            return TQ_ERR_LAUNCH;
     }
     return TQ_OK;
 }
