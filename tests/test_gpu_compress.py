@@ -330,3 +330,44 @@ def test_compress_paged_strided_rows_match_contiguous(dtype):
     compress_and_scatter(key.contiguous(), val.contiguous(), b, slots, books, bs)
     assert _native.read_status(DEV) == 0
     assert torch.equal(a, b)
+
+
+def test_compress_paged_random_shapes_vs_oracle():
+    """Seeded sweep over shapes, formats, dtypes and block sizes: pre-rotated inputs must match the oracle bit for
+    bit (indices, signs), rotated ones within the 1e-4 allowance; norms within one fp16 ulp."""
+    rng = np.random.default_rng(1234)
+    fmts = [CacheFormat.named(n) for n in ("turbo2", "turbo3", "turbo4")] + [CacheFormat(4, 2, True), CacheFormat(2, 4, False)]
+    for case in range(24):
+        fmt = fmts[case % len(fmts)]
+        books = Codebooks(fmt, DEV)
+        T = int(rng.integers(1, 200))
+        Hkv = int(rng.choice([1, 2, 3, 5, 8]))
+        bs = int(rng.choice([16, 32, 64]))
+        dtype = [torch.float16, torch.bfloat16, torch.float32][case % 3]
+        prerotated = bool(case & 1)
+        nb = (T + bs - 1) // bs + 1
+        g = torch.Generator().manual_seed(100 + case)
+        key = (torch.randn(T, Hkv, 128, generator=g) * float(rng.choice([1e-3, 1.0, 30.0]))).to(dtype)
+        val = torch.randn(T, Hkv, 128, generator=g).to(dtype)
+        slots = torch.randperm(nb * bs, generator=g)[:T]
+        cache = allocate_cache(nb, bs, Hkv, fmt, DEV)
+        compress_and_scatter(key.to(DEV), val.to(DEV), cache, slots.to(DEV), books, bs, prerotated=prerotated)
+        assert _native.read_status(DEV) == 0, case
+        f = paged_layout.unpack_cache(cache.cpu(), bs, fmt.k_bits, fmt.v_bits, fmt.use_qjl)
+        H = None if prerotated else O.make_wht_matrix(128)
+        ok = O.polarquant_compress(key.float().numpy().reshape(-1, 128), books.kc.cpu().numpy(), books.kb.cpu().numpy(),
+                                   fmt.k_bits, fmt.use_qjl, H)
+        ov = O.polarquant_compress(val.float().numpy().reshape(-1, 128), books.vc.cpu().numpy(), books.vb.cpu().numpy(),
+                                   fmt.v_bits, False, H)
+        blk, off = slots // bs, slots % bs
+        got_k = f["k_idx"][blk, off].numpy().reshape(-1, 128)
+        got_v = f["v_idx"][blk, off].numpy().reshape(-1, 128)
+        tol = 0.0 if prerotated else 1e-3          # small cases: one flipped coordinate in 128 T Hkv can exceed 1e-4
+        assert (got_k != ok["indices"]).mean() <= tol, (case, "k_idx")
+        assert (got_v != ov["indices"]).mean() <= tol, (case, "v_idx")
+        assert _half_ulp_close(f["k_norm"][blk, off].reshape(-1), ok["norms"]), (case, "k_norm")
+        assert _half_ulp_close(f["v_norm"][blk, off].reshape(-1), ov["norms"]), (case, "v_norm")
+        if fmt.use_qjl:
+            got_s = f["k_signs"][blk, off].numpy().reshape(-1, 128)
+            assert (got_s != (ok["signs"] > 0)).mean() <= tol, (case, "signs")
+            assert _half_ulp_close(f["k_rnorm"][blk, off].reshape(-1), ok["rot_residual_norm"], max_ulp=2), (case, "rnorm")
