@@ -636,8 +636,26 @@ __global__ void __launch_bounds__(kFastWarps * 32, TQ_CMP_MINBLOCKS) compress_pa
     }
 }
 
+// Small launches (the new tokens of one decode step): no tables to build, one group of 32 items per CTA.
+template <int KB, int VB, bool QJL>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) compress_paged_small_kernel(const PagedParams p) {
+    __shared__ float csm[1 << KB];
+    if (threadIdx.x < (1 << KB)) csm[threadIdx.x] = p.kc[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2);
+    compress_items_generic<KB, VB, QJL>(p, item, lane, csm);
+}
+
+constexpr int64_t kSmallLaunchItems = 2048;   // below this the table set-up of the fast kernel costs more than it saves
+
 template <int KB, int VB, bool QJL>
 int launch_paged_fast(const PagedParams& p, cudaStream_t st) {
+    if (p.n_items <= kSmallLaunchItems) {
+        const unsigned grid = static_cast<unsigned>((p.n_items + kItemsPerCta - 1) / kItemsPerCta);
+        compress_paged_small_kernel<KB, VB, QJL><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+        return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    }
     const int64_t n_groups = (p.n_items + kFastItemsPerCta - 1) / kFastItemsPerCta;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return TQ_ERR_LAUNCH;
