@@ -149,8 +149,82 @@ def test_decode_bad_block_table_is_flagged_not_fatal():
         paged_decode_attention(q, cache, bt, torch.tensor([40], dtype=torch.int32, device=DEV), books, 32)
 
 
+@pytest.mark.parametrize("chunk", [0, 2])
+def test_decode_length_beyond_block_table_is_cut_and_flagged(chunk):
+    """A sequence length larger than the block table can describe: the walk stops at the table's width (and the
+    chunk count at the workspace's), the status word says so, the result is the attention over the covered part."""
+    fmt = CacheFormat.named("turbo3")
+    books = Codebooks(fmt, DEV)
+    f = random_fields(fmt, 12, 16, 2, 31)
+    cache = paged_layout.pack_cache(f, 16, 3, 3, True).to(DEV)
+    g = torch.Generator().manual_seed(32)
+    bt = torch.randperm(12, generator=g)[:8].reshape(2, 4).to(torch.int32)
+    q = torch.randn(2, 8, 128, generator=g).half()
+    lens_bad = torch.tensor([4 * 16 + 300, 50], dtype=torch.int32)
+    out = paged_decode_attention(q.to(DEV), cache, bt.to(DEV), lens_bad.to(DEV), books, 16, chunk_pages=chunk)
+    torch.cuda.synchronize()
+    assert _native.read_status(DEV) == _native.STATUS_BAD_BLOCK
+    lens_cut = torch.tensor([64, 50], dtype=torch.int32)
+    ref = oracle_decode(q, None, f, fmt, books, bt, lens_cut, 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128, 16)
+    assert_attn_close(out.float().cpu().numpy(), ref)
+    # the same cut when the host states the longest sequence instead of relying on the table's width
+    wide = torch.zeros(2, 40, dtype=torch.int32)
+    wide[:, :4] = bt
+    out2 = paged_decode_attention(q.to(DEV), cache, wide.to(DEV), lens_cut.to(DEV), books, 16, chunk_pages=chunk,
+                                  max_seq_len=64)
+    assert _native.read_status(DEV) == 0
+    assert_attn_close(out2.float().cpu().numpy(), ref)
+
+
+def _slice_case(fmt, lens, G, thresh, qscale, seed, bias_pages=0.0):
+    """One KV head, `G` query heads, sequences of the given lengths over a shared random page pool."""
+    books = Codebooks(fmt, DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    pages = [(n + 15) // 16 for n in lens]
+    nb = sum(pages) + 2
+    f = random_fields(fmt, nb, 16, 1, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    perm = torch.randperm(nb, generator=g)
+    bt = torch.zeros(len(lens), max(pages), dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(pages):
+        bt[i, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    if bias_pages > 0:
+        # a few pages whose keys line up with the query far better than the rest: large norms make their logits peak
+        hot = torch.rand(nb, generator=g) < bias_pages
+        f["k_norm"][hot] = (f["k_norm"][hot].float() * 3).half()
+    cache = paged_layout.pack_cache(f, 16, fmt.k_bits, fmt.v_bits, fmt.use_qjl).to(DEV)
+    q = (torch.randn(len(lens), G, 128, generator=g) * qscale).half()
+    sm, cs = 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128
+    stats = torch.zeros(2, dtype=torch.int32, device=DEV) if thresh > 0 else None
+    out = paged_decode_attention(q.to(DEV), cache, bt.to(DEV), lens_t.to(DEV), books, 16, sm, cs, sparse_thresh=thresh,
+                                 skip_stats=stats)
+    torch.cuda.synchronize()
+    assert _native.read_status(DEV) == 0
+    ref = oracle_decode(q, None, f, fmt, books, bt, lens_t, sm, cs, 16)        # dense fp32 truth
+    return out.float().cpu().numpy(), ref, (None if stats is None else stats.cpu().tolist())
+
+
+def test_long_sparse_sequence_slice_vs_oracle():
+    """The shape of the high-concurrency long-context workload for one (sequence, KV head): 32768 tokens
+    (2048 pages, split into chunks), GQA 8, turbo3, Sparse-V threshold 1e-6 with a peaked softmax."""
+    out, ref, stats = _slice_case(CacheFormat.named("turbo3"), [32768, 16384 + 5], 8, 1e-6, 2.0, 41, bias_pages=0.02)
+    assert_attn_close(out, ref)
+    assert stats[0] == 2048 + 1025 and stats[1] > 0                              # pages were really skipped
+    out_d, ref_d, _ = _slice_case(CacheFormat.named("turbo3"), [32768, 16384 + 5], 8, 0.0, 2.0, 41, bias_pages=0.02)
+    assert_attn_close(out_d, ref_d)
+
+
+def test_mixed_length_turbo2_slice_vs_oracle():
+    """The shape of the mixed-length workload for one KV head: turbo2 (2-bit + QJL), GQA 4, lengths from 128 to
+    65536 tokens (4096 pages, 16 chunks) in one batch."""
+    out, ref, _ = _slice_case(CacheFormat.named("turbo2"), [65536, 128, 4096, 1500, 9000], 4, 0.0, 1.0, 43)
+    assert_attn_close(out, ref)
+
+
 def test_config2_compress_then_decode():
-    """BASELINE config 2: turbo4, 32 query / 8 KV heads, context 4096, block 16, permuted block table,
+    """turbo4 single-sequence round trip: 32 query / 8 KV heads, context 4096, block 16, permuted block table,
     fp16 K/V with 4 outlier channels x10, one decode step; compress with the CUDA kernel, then decode."""
     fmt = CacheFormat.named("turbo4")
     books = Codebooks(fmt, DEV)
@@ -277,7 +351,7 @@ def test_sparse_v_wrapper_on_reference_layout_cache():
 
 
 def test_full_size_decode_properties():
-    """BASELINE config 3 shape for one layer (64 x 8192 tokens, 64q/8kv, turbo3, cache written by the compress
+    """The batched-decode workload at full size for one layer (64 x 8192 tokens, 64q/8kv, turbo3, cache written by the compress
     kernel): results do not depend on the split-K chunking, on where pages sit in the pool, or on a common
     power-of-two scale of V; a slice of the batch matches the oracle."""
     fmt = CacheFormat.named("turbo3")

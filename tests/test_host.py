@@ -173,6 +173,20 @@ def test_launchers_validate_arguments_without_touching_a_gpu():
                              null, null, 2, 8, 8, 1, 3, 3, 1, 0, null) == -1
 
 
+def test_head_counts_that_form_no_query_group_are_refused_on_the_host():
+    """Fewer query heads than KV heads (or a non-multiple) used to make the chunk-size search loop for ever."""
+    L = _native.lib()
+    null = ctypes.c_void_p(0)
+    assert L.tq_decode_auto_chunk_pages(4, 8, 4, 100) == -1
+    assert L.tq_decode_auto_chunk_pages(4, 8, 12, 100) == -1
+    assert L.tq_decode_workspace_bytes(4, 4, 8, 100, 0) == -1
+    assert L.tq_decode_workspace_bytes(4, 12, 8, 100, 16) == -1
+    assert L.tq_decode_paged_static(null, null, null, 0, null, 1, 16, null, 1, null, null, null, 1.0, 1.0, 0.0,
+                                    null, null, 2, 4, 8, 100, 3, 3, 1, 0, null) == -1
+    assert L.tq_decode_paged_static(null, null, null, 0, null, 1, 16, null, 1, null, null, null, 1.0, 1.0, 0.0,
+                                    null, null, 0, 4, 8, 100, 3, 3, 1, 0, null) == 0      # zero sequences
+
+
 def test_no_cpu_fallback():
     x = torch.randn(4, 128)
     c, b = make_codebook(128, 3)

@@ -64,3 +64,17 @@ def test_vllm_backend_registers_under_custom():
     assert impl.fused_rope_kvcache_supported() is False
     with pytest.raises(NotImplementedError):
         Bk.get_impl_cls()(32, 128, 0.088, 8, sliding_window=128)
+
+
+def test_split_batch_sorts_decodes_prefills_and_refuses_extends():
+    """One step of a v1 engine mixes running decodes with new prefills (the reference splits by
+    num_decodes / num_prefills, tq_fp4_backend.py:517-530)."""
+    # requests: decode (len 301), prefill of 40, decode (len 78), one-token sequence, padding request
+    qsl = [0, 1, 41, 42, 43, 43]
+    lens = [301, 40, 78, 1, 0]
+    dec, pre = B.split_batch(qsl, lens)
+    assert dec == [(0, 0), (2, 41)]
+    assert pre == [(1, 1, 41), (3, 42, 43)]
+    assert B.split_batch([0, 1, 2], [9, 10]) == ([(0, 0), (1, 1)], [])
+    with pytest.raises(NotImplementedError):
+        B.split_batch([0, 5], [25])            # five new tokens over twenty cached ones

@@ -1,13 +1,16 @@
 """tq_decode_paged_static: decode for hosts that cannot allocate device memory (all HBM already given to
 a KV-cache pool, or a binding that owns no device allocator).  Called through the C ABI with ctypes and held
-to the output of tq_decode_paged on the same inputs, twice in a row with different problems so that whatever
-the first call left in the library's fixed scratch array is there when the second one runs."""
+to the output of tq_decode_paged on the same inputs and to the CPU oracle, twice in a row with different
+problems so that whatever the first call left in the library's fixed scratch array is there when the second one
+runs; the device's free memory and torch's allocator are read before and after to show that nothing was allocated."""
 import ctypes
 import math
 
+import numpy as np
 import pytest
 import torch
 
+from oracle import tq_oracle as O
 from turboquant.kernels import _native, paged_layout
 from turboquant.kernels.paged import CacheFormat, Codebooks
 
@@ -17,12 +20,7 @@ SCRATCH_BYTES = 16 * 1024 * 1024
 
 
 def _bind():
-    L = _native.lib()
-    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
-    L.tq_decode_paged_static.argtypes = [vp, vp, vp, i32, vp, i64, i32, vp, i64, vp, vp, vp, f32, f32, f32,
-                                         vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
-    L.tq_decode_paged_static.restype = i32
-    return L
+    return _native.lib()          # declares the argument types of both decode entry points
 
 
 def _problem(seed, lens, Hq, Hkv, fmt):
@@ -41,7 +39,7 @@ def _problem(seed, lens, Hq, Hkv, fmt):
     cache = paged_layout.pack_cache(f, bs, fmt.k_bits, fmt.v_bits, fmt.use_qjl).to(DEV)
     bt = torch.randperm(nb, generator=g).reshape(ns, max_blocks).to(torch.int32).to(DEV)
     q = torch.randn(ns, Hq, 128, generator=g).half().to(DEV)
-    return cache, bt, lens.to(DEV), q, nb, max_blocks
+    return cache, bt, lens.to(DEV), q, nb, max_blocks, f
 
 
 def _call(L, static, out, q, cache, bt, lens, books, fmt, nb, max_pages, chunk_pages, ws=None):
@@ -64,27 +62,43 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
     # two different problems back to back: many chunks per sequence, so the split-K partials really go
     # through the scratch, and the second problem is smaller so stale partials of the first stay behind it
     for seed, lens, Hq, Hkv, chunk in ((1, [900, 333, 64, 1], 16, 2, 4), (2, [130, 700], 8, 1, 7)):
-        cache, bt, lens_d, q, nb, max_blocks = _problem(seed, lens, Hq, Hkv, fmt)
+        cache, bt, lens_d, q, nb, max_blocks, f = _problem(seed, lens, Hq, Hkv, fmt)
         need = L.tq_decode_workspace_bytes(len(lens), Hq, Hkv, max_blocks, chunk)
         assert 0 < need <= SCRATCH_BYTES
         ws = torch.empty(need, dtype=torch.uint8, device=DEV)
         ref = torch.empty_like(q)
         got = torch.empty_like(q)
         assert _call(L, False, ref, q, cache, bt, lens_d, books, fmt, nb, max_blocks, chunk, ws) == 0
+        # the entry point's first call on a device looks up the scratch array's address (and the driver may load
+        # the kernels' module then): measure around a call made after that
         assert _call(L, True, got, q, cache, bt, lens_d, books, fmt, nb, max_blocks, chunk) == 0
         torch.cuda.synchronize()
+        got.zero_()
+        free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        assert _call(L, True, got, q, cache, bt, lens_d, books, fmt, nb, max_blocks, chunk) == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == torch_before
         assert torch.isfinite(got.float()).all()
         d = (got.float() - ref.float()).abs()
         # the same kernels run on the same data: the tests' attention tolerance, in practice identical
         assert (d - 1e-2 * ref.float().abs()).max().item() <= 2e-3
         assert torch.equal(got, ref)
+        # and against the CPU oracle on the same logical cache contents
+        kf = {"idx": f["k_idx"].numpy(), "norm": f["k_norm"].float().numpy(), "signs": f["k_signs"].numpy(),
+              "rnorm": f["k_rnorm"].float().numpy()}
+        vf = {"idx": f["v_idx"].numpy(), "norm": f["v_norm"].float().numpy()}
+        want = O.paged_decode(q.float().cpu().numpy(), q.float().cpu().numpy(), kf, vf, bt.cpu().numpy(),
+                              np.asarray(lens), books.kc.cpu().numpy(), books.vc.cpu().numpy(), 1 / math.sqrt(128),
+                              math.sqrt(math.pi / 2) / 128, 16)
+        dd = np.abs(got.float().cpu().numpy() - want)
+        assert (dd - 1e-2 * np.abs(want)).max() <= 2e-3
 
 
 def test_static_scratch_refuses_what_does_not_fit():
     L = _bind()
     fmt = CacheFormat.named("turbo3")
     books = Codebooks(fmt, DEV)
-    cache, bt, lens_d, q, nb, max_blocks = _problem(3, [64, 64], 8, 1, fmt)
+    cache, bt, lens_d, q, nb, max_blocks, _ = _problem(3, [64, 64], 8, 1, fmt)
     out = torch.empty_like(q)
     # claim a problem whose partials exceed the 16 MiB array: refused before any launch, output untouched
     out.fill_(7.0)

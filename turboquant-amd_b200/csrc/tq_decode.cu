@@ -96,6 +96,7 @@ struct DecodeParams {
     int sub_shift;           // log2(block_size / 16)
     int64_t block_stride;    // bytes between consecutive blocks of the cache
     int chunk_pages, max_chunks;
+    int max_pages;           // pages per sequence the block table and the workspace were sized for
     int io_dtype;
     int share_tables;        // K and V use the same codebook: one pair table serves both
     int rotate_q;            // the query is in original space: rotate it (fast WHT) while loading
@@ -292,7 +293,10 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     const int kvh = blockIdx.y / p.ngroups, qg = blockIdx.y % p.ngroups;
     const int seq = blockIdx.z;
     const int L = p.seq_lens[seq];
-    const int npages = (L + kPageTokens - 1) / kPageTokens;
+    // A length beyond what the block table and the workspace were sized for is cut to that size and flagged:
+    // the walk never leaves the table row and a chunk index never leaves the workspace.
+    const bool too_long = L > p.max_pages * kPageTokens;
+    const int npages = too_long ? p.max_pages : (L + kPageTokens - 1) / kPageTokens;
     const int g_in_group = qg * 8 + gid;                // query index inside the GQA group
     const int nq = min(8, p.G - qg * 8);                // live query heads in this CTA
     const int head0 = kvh * p.G + qg * 8;
@@ -603,7 +607,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 
     if (p.status) {
         int bits = 0;
-        if (__any_sync(0xffffffffu, bad_block)) bits |= TQ_STATUS_BAD_BLOCK;
+        if (__any_sync(0xffffffffu, bad_block) || too_long) bits |= TQ_STATUS_BAD_BLOCK;
         if (__any_sync(0xffffffffu, timed_out)) bits |= TQ_STATUS_TIMEOUT;
         if (bits && lane == 0) atomicOr(p.status, bits);
     }
@@ -675,7 +679,7 @@ __global__ void __launch_bounds__(kHeadDim) decode_merge_kernel(const DecodePara
     pdl_release_and_wait();
     const int head = blockIdx.x, seq = blockIdx.y, dim = threadIdx.x;
     const int L = p.seq_lens[seq];
-    const int npages = (L + kPageTokens - 1) / kPageTokens;
+    const int npages = min((L + kPageTokens - 1) / kPageTokens, p.max_pages);   // same cut as the partial kernel
     const int nchunks = (npages + p.chunk_pages - 1) / p.chunk_pages;
     if (nchunks <= 1) return;  // written by the partial kernel
     const int kvh = head / p.G, gi = head % p.G;
@@ -747,6 +751,7 @@ using namespace tq;
 
 extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int num_q_heads, int max_pages_per_seq) {
     if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;   // also num_q_heads < num_kv_heads: no query group
     // Sizes come from the longest sequence; chunks beyond a shorter sequence's end exit at once.
     // Measured on batch 64 x 8192 tokens with 1, 2, 4 and 8 KV heads per GPU (chunk sizes 32..512 pages):
     //  * about 1024 CTAs (1.7 waves of 148 SMs x 4 CTAs) is the flat optimum, with a power-of-two number
@@ -781,6 +786,7 @@ extern "C" int tq_decode_auto_chunk_pages(int num_seqs, int num_kv_heads, int nu
 extern "C" int64_t tq_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq,
                                              int chunk_pages) {
     if (num_seqs <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
     if (chunk_pages <= 0) chunk_pages = tq_decode_auto_chunk_pages(num_seqs, num_kv_heads, num_q_heads, max_pages_per_seq);
     const int G = num_q_heads / num_kv_heads;
     const int ngroups = (G + 7) / 8;
@@ -845,6 +851,7 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
                      page_bytes(k_bits, v_bits, use_qjl ? 1 : 0);
     p.chunk_pages = chunk_pages;
     p.max_chunks = max_chunks;
+    p.max_pages = max_pages_per_seq;
     p.io_dtype = io_dtype;
     p.rotate_q = rotate_q;
     p.derotate_out = derotate_out;
@@ -918,6 +925,7 @@ extern "C" int tq_decode_paged_static(void* out, const void* q_rot, const void* 
                                       int chunk_pages, tq_stream_t stream) {
     if (num_seqs == 0) return TQ_OK;
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0) return TQ_ERR_ARG;
+    if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
     if (chunk_pages <= 0) chunk_pages = tq_decode_auto_chunk_pages(num_seqs, num_kv_heads, num_q_heads, max_pages_per_seq);
     // Refuse, before touching the GPU, any problem whose split-K partials do not fit the fixed array.
     const int64_t need = tq_decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, max_pages_per_seq, chunk_pages);

@@ -12,9 +12,10 @@ prefill runs ordinary attention on the raw K/V of the step.  Differences:
     (TurboQuant packed pages), not FP4 nibbles plus side buffers of scales.
 
 The classes are built on first use so that importing this module does not import vLLM.
-Status: written against vLLM 0.22's v1 interface and exercised here only up to
-class construction and the pure functions below; it has not been run inside a
-vLLM engine.  Chunked prefill with cached context is not supported (it raises).
+Status: written against vLLM 0.22's v1 interface.  `do_kv_cache_update` and `forward` are exercised
+on a GPU with hand-built layer and metadata objects (decode, fresh prefill and steps that mix both);
+they have not been run inside a vLLM engine.  A step may mix decode rows (one new token over cached
+context) with fresh prefills; a prefill chunk that continues cached context (an "extend") raises.
 """
 from __future__ import annotations
 
@@ -43,6 +44,32 @@ def kv_cache_shape(num_blocks: int, block_size: int, num_kv_heads: int, head_siz
     if block_size not in (16, 32):
         raise ValueError("block_size must be 16 or 32")
     return (fmt or cache_format_from_env()).cache_shape(num_blocks, block_size, num_kv_heads)
+
+
+def split_batch(query_start_loc: list, seq_lens: list) -> tuple[list, list]:
+    """Sort the requests of one step into decode rows and fresh prefills.
+
+    query_start_loc [n + 1] and seq_lens [n] are host lists.  Request i owns query tokens
+    query_start_loc[i] .. query_start_loc[i + 1]; it is a decode when it has one query token (its sequence
+    length counts that token), a fresh prefill when its query tokens are its whole sequence.  Returns
+    (decodes, prefills): decodes = [(request, token_row)], prefills = [(request, first_row, end_row)].
+    Anything else continues cached context with more than one token and raises NotImplementedError
+    (the reference serves those through its extend branch, tq_fp4_backend.py:555-601).  Requests without
+    query tokens (padding) are dropped.
+    """
+    decodes, prefills = [], []
+    for i in range(len(query_start_loc) - 1):
+        a, b = int(query_start_loc[i]), int(query_start_loc[i + 1])
+        n, total = b - a, int(seq_lens[i])
+        if n <= 0:
+            continue
+        if n == total:
+            prefills.append((i, a, b))       # includes a one-token sequence: attention over itself
+        elif n == 1:
+            decodes.append((i, a))
+        else:
+            raise NotImplementedError("chunked prefill over cached context is not supported")
+    return decodes, prefills
 
 
 _classes = None
@@ -99,23 +126,33 @@ def _build_classes():
             n = attn_metadata.num_actual_tokens
             q = query[:n].view(n, self.num_heads, self.head_size)
             out = output[:n].view(n, self.num_heads, self.head_size)
+            max_seq_len = int(getattr(attn_metadata, "max_seq_len", 0) or 0)
             if attn_metadata.max_query_len == 1:
                 # decode: one token per sequence, attention over the packed cache (tq_fp4_backend.py:604-641)
                 state = self._state(layer, q.device)
                 block_size = kv_cache.shape[2] // self.format.page_bytes * 16
                 res = paged_decode_attention(q.contiguous(), kv_cache, attn_metadata.block_table[:n],
                                              attn_metadata.seq_lens[:n], state.books, block_size,
-                                             sm_scale=self.scale, rotate_q=True, derotate_out=True)
+                                             sm_scale=self.scale, rotate_q=True, derotate_out=True,
+                                             max_seq_len=max_seq_len)
                 out.copy_(res)
                 return output
-            # prefill on the raw K/V of this step (tq_fp4_backend.py:532-553); every sequence must start at 0
-            starts = attn_metadata.query_start_loc.tolist()
-            lens = attn_metadata.seq_lens.tolist()
+            # A step with prefills: sort the requests on the host (the reference's metadata carries
+            # num_decodes / num_prefills for this, tq_fp4_backend.py:517-530).
+            decodes, prefills = split_batch(attn_metadata.query_start_loc.tolist(), attn_metadata.seq_lens.tolist())
+            if decodes:
+                state = self._state(layer, q.device)
+                block_size = kv_cache.shape[2] // self.format.page_bytes * 16
+                req = torch.tensor([r for r, _ in decodes], dtype=torch.long, device=q.device)
+                rows = torch.tensor([t for _, t in decodes], dtype=torch.long, device=q.device)
+                res = paged_decode_attention(q[rows].contiguous(), kv_cache, attn_metadata.block_table[req].contiguous(),
+                                             attn_metadata.seq_lens[req].contiguous(), state.books, block_size,
+                                             sm_scale=self.scale, rotate_q=True, derotate_out=True,
+                                             max_seq_len=max_seq_len)
+                out[rows] = res
+            # prefill on the raw K/V of this step (tq_fp4_backend.py:532-553)
             g = self.num_heads // self.num_kv_heads
-            for i in range(len(starts) - 1):
-                a, b = starts[i], starts[i + 1]
-                if b - a != lens[i]:
-                    raise NotImplementedError("chunked prefill over cached context is not supported")
+            for _, a, b in prefills:
                 qs = q[a:b].transpose(0, 1).unsqueeze(0)
                 ks = key[a:b].view(b - a, self.num_kv_heads, self.head_size).repeat_interleave(g, 1).transpose(0, 1).unsqueeze(0)
                 vs = value[a:b].view(b - a, self.num_kv_heads, self.head_size).repeat_interleave(g, 1).transpose(0, 1).unsqueeze(0)

@@ -7,7 +7,7 @@ TQ_FP4_PA_SO plays in the reference, turboquant/integration/tq_fp4_backend.py:59
 Ops registered (namespace `tq_b200`):
   compress_paged(key, value, cache, slot_mapping, kc, kb, vc, vb, block_size, k_bits, v_bits, use_qjl, prerotated)
   decode_paged(q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale, sparse_thresh,
-               block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags) -> out
+               block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags, max_seq_len) -> out
   wht_rows(x, scale) -> x @ H * scale
 """
 from __future__ import annotations
@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
     L.tq_decode_workspace_bytes.restype = i64
     L.tq_decode_paged.argtypes = [vp, vp, vp, i32, vp, i64, i32, vp, i64, vp, vp, vp, f32, f32, f32, vp, i64,
                                   vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    L.tq_decode_paged_static.argtypes = [vp, vp, vp, i32, vp, i64, i32, vp, i64, vp, vp, vp, f32, f32, f32,
+                                         vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]
     L.tq_wht_rows.argtypes = [vp, vp, i32, i64, f32, vp]
     L.tq_compress_k.argtypes = [vp, i32, i64, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp]
     L.tq_compress_v.argtypes = [vp, i32, i64, vp, i32, i32, vp, vp, vp]
@@ -67,7 +69,7 @@ def lib() -> ctypes.CDLL:
     L.tq_packed_attention_auto_splits.argtypes = [i32, i32]
     L.tq_packed_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, f32, i32, i32, i32, i32, vp, i64, vp, vp]
     for name in ("tq_page_bytes", "tq_compress_paged", "tq_decode_auto_chunk_pages", "tq_decode_paged",
-                 "tq_wht_rows", "tq_compress_k", "tq_compress_v", "tq_polarquant_compress",
+                 "tq_decode_paged_static", "tq_wht_rows", "tq_compress_k", "tq_compress_v", "tq_polarquant_compress",
                  "tq_packed_attention_auto_splits", "tq_packed_attention"):
         getattr(L, name).restype = i32
     _lib = L
@@ -196,7 +198,13 @@ def decode_chunk_pages(num_seqs: int, num_kv_heads: int, num_q_heads: int, max_p
 
 def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale,
                        sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, skip_stats=None,
-                       io_flags: int = 0) -> None:
+                       io_flags: int = 0, max_seq_len: int = 0, static_scratch: bool = False) -> None:
+    """Checked call of tq_decode_paged (or, with static_scratch, of tq_decode_paged_static, which keeps the
+    split-K partials in the library's fixed device array and allocates nothing).
+
+    max_seq_len > 0 is the longest sequence of this step as the host knows it: grid, chunk size and workspace are
+    then sized for it instead of for the width of the block table (an engine hands over a table as wide as its
+    maximum model length).  Lengths beyond it are cut by the kernel and flagged STATUS_BAD_BLOCK."""
     dev = _require_cuda(out, q_rot, cache, block_tables, seq_lens, kc, vc)
     if q_rot.dim() != 3 or q_rot.shape[-1] != 128 or not q_rot.is_contiguous():
         raise ValueError("q must be contiguous [num_seqs, q_heads, 128]")
@@ -228,6 +236,8 @@ def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc
         if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
             raise ValueError(f"{name} must be contiguous fp32 with {n} entries")
     max_pages = block_tables.shape[1] * sub
+    if max_seq_len > 0:
+        max_pages = max(1, min(max_pages, (int(max_seq_len) + 15) // 16))
     L = lib()
     if chunk_pages <= 0:
         chunk_pages = L.tq_decode_auto_chunk_pages(ns, Hkv, Hq, max_pages)
@@ -237,10 +247,13 @@ def _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc
             _ptr(block_tables), block_tables.stride(0), _ptr(seq_lens), _ptr(kc), _ptr(vc),
             float(sm_scale), float(corr_scale), float(sparse_thresh))
     with torch.cuda.device(dev):
-        need = L.tq_decode_workspace_bytes(ns, Hq, Hkv, max_pages, chunk_pages)
-        ws = workspace(dev, need)
-        rc = L.tq_decode_paged(*head, _ptr(ws), ws.numel(), *common_tail)
-    _check(rc, "tq_decode_paged")
+        if static_scratch:
+            rc = L.tq_decode_paged_static(*head, *common_tail)
+        else:
+            need = L.tq_decode_workspace_bytes(ns, Hq, Hkv, max_pages, chunk_pages)
+            ws = workspace(dev, need)
+            rc = L.tq_decode_paged(*head, _ptr(ws), ws.numel(), *common_tail)
+    _check(rc, "tq_decode_paged_static" if static_scratch else "tq_decode_paged")
 
 
 def wht_rows(x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -303,16 +316,18 @@ def _(key, value, cache, slot_mapping, kc, kb, vc, vb, block_size, k_bits, v_bit
 def decode_paged_op(q_rot: torch.Tensor, q_proj: Optional[torch.Tensor], cache: torch.Tensor,
                     block_tables: torch.Tensor, seq_lens: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor,
                     sm_scale: float, corr_scale: float, sparse_thresh: float, block_size: int, k_bits: int,
-                    v_bits: int, use_qjl: bool, chunk_pages: int, io_flags: int = 0) -> torch.Tensor:
+                    v_bits: int, use_qjl: bool, chunk_pages: int, io_flags: int = 0,
+                    max_seq_len: int = 0) -> torch.Tensor:
     out = torch.empty_like(q_rot)
     _decode_paged_impl(out, q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale,
-                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags=io_flags)
+                       sparse_thresh, block_size, k_bits, v_bits, use_qjl, chunk_pages, io_flags=io_flags,
+                       max_seq_len=max_seq_len)
     return out
 
 
 @decode_paged_op.register_fake
 def _(q_rot, q_proj, cache, block_tables, seq_lens, kc, vc, sm_scale, corr_scale, sparse_thresh, block_size,
-      k_bits, v_bits, use_qjl, chunk_pages, io_flags=0):
+      k_bits, v_bits, use_qjl, chunk_pages, io_flags=0, max_seq_len=0):
     return torch.empty_like(q_rot)
 
 

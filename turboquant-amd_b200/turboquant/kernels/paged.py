@@ -93,7 +93,8 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
                            corr_scale: Optional[float] = None, sparse_thresh: float = 0.0,
                            q_proj: Optional[torch.Tensor] = None, rotate_q: bool = False,
                            derotate_out: bool = False, chunk_pages: int = 0,
-                           out: Optional[torch.Tensor] = None, skip_stats: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, skip_stats: Optional[torch.Tensor] = None,
+                           max_seq_len: int = 0, static_scratch: bool = False) -> torch.Tensor:
     """One decode step over the packed paged cache.
 
     q [num_seqs, Hq, 128] fp16/bf16.  With rotate_q the query is first taken to
@@ -102,6 +103,9 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
     unless derotate_out.  sm_scale defaults to 1/sqrt(128), corr_scale to
     sqrt(pi/2)/128.  sparse_thresh > 0 turns on the Sparse-V page skip.
     skip_stats: optional uint32[2] device tensor accumulating (pages visited, pages skipped).
+    max_seq_len: the longest sequence of the step when the host knows it (a serving engine does); the launch is
+    then sized for it rather than for the width of block_tables.  static_scratch: keep the split-K partials in
+    the library's fixed 16 MiB device array instead of a torch workspace (no allocation; larger problems raise).
     """
     fmt = books.fmt
     if sm_scale is None:
@@ -121,12 +125,14 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
         block_tables = block_tables.to(torch.int32)
     if seq_lens.dtype != torch.int32:
         seq_lens = seq_lens.to(torch.int32)
-    if out is None and skip_stats is None:
+    if out is None and skip_stats is None and not static_scratch:
         return torch.ops.tq_b200.decode_paged(q_in, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc,
                                               books.vc, float(sm_scale), float(corr_scale), float(sparse_thresh),
-                                              block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, int(chunk_pages), flags)
+                                              block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, int(chunk_pages), flags,
+                                              int(max_seq_len))
     res = out if out is not None else torch.empty_like(q_in)
     _native._decode_paged_impl(res, q_in, q_proj, cache, block_tables, seq_lens.contiguous(), books.kc, books.vc,
                                sm_scale, corr_scale, sparse_thresh, block_size, fmt.k_bits, fmt.v_bits,
-                               fmt.use_qjl, int(chunk_pages), skip_stats=skip_stats, io_flags=flags)
+                               fmt.use_qjl, int(chunk_pages), skip_stats=skip_stats, io_flags=flags,
+                               max_seq_len=int(max_seq_len), static_scratch=static_scratch)
     return res
