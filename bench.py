@@ -299,6 +299,7 @@ def time_device_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     if stats is not None:
         seen, skipped = stats.cpu().tolist()
         skip = {"v_pages_seen": seen, "v_pages_skipped": skipped, "fraction": (skipped / seen if seen else 0.0)}
+    time_device_steps.last_queries = q_dev
     return ms, skip, outs
 
 
@@ -385,6 +386,114 @@ def time_e2e_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
     return e0.elapsed_time(e1), h2d, d2h, how
 
 
+def parity_slice(wl: "Workload", outs: torch.Tensor, q_dev: torch.Tensor, layer: int = 0, seq: int = 3, kvh: int = 0):
+    """Error of one (sequence, KV head) slice of the timed workload's output against the CPU oracle (the checker
+    role of oracle/: computed after the timed region, never inside it).  Returns max-abs and max-rel error."""
+    from oracle import tq_oracle as O
+    from turboquant.kernels import paged_layout
+    f = wl.fmt
+    n_pages = int(wl.pages[seq])
+    L = int(wl.lens[seq])
+    g = wl.hq // wl.hkv
+    pages = wl.caches[layer][wl.block_tables[seq, :n_pages].long(), kvh].cpu()
+    u = paged_layout.unpack_pages(pages, f.k_bits, f.v_bits, f.use_qjl)
+    kf = {"idx": u["k_idx"].reshape(-1, 16, 1, 128).numpy(), "norm": u["k_norm"].float().reshape(-1, 16, 1).numpy()}
+    if f.use_qjl:
+        kf["signs"] = u["k_signs"].reshape(-1, 16, 1, 128).numpy()
+        kf["rnorm"] = u["k_rnorm"].float().reshape(-1, 16, 1).numpy()
+    vf = {"idx": u["v_idx"].reshape(-1, 16, 1, 128).numpy(), "norm": u["v_norm"].float().reshape(-1, 16, 1).numpy()}
+    qs = q_dev[layer, seq:seq + 1, kvh * g:(kvh + 1) * g].float().cpu().numpy()
+    ref = O.paged_decode(qs, qs, kf, vf, np.arange(n_pages)[None], np.array([L]), wl.books.kc.cpu().numpy(),
+                         wl.books.vc.cpu().numpy(), 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128, 16)[0]
+    got = outs[layer, seq, kvh * g:(kvh + 1) * g].float().cpu().numpy()
+    d = np.abs(got - ref)
+    return {"slice": f"layer {layer}, sequence {seq} ({L} tokens), KV head {kvh}, {g} query heads", "max_abs": float(d.max()),
+            "max_rel": float((d / np.maximum(np.abs(ref), 1e-6))[np.abs(ref) > 1e-3].max()) if (np.abs(ref) > 1e-3).any() else 0.0,
+            "max_abs_minus_1e-2_ref": float((d - 1e-2 * np.abs(ref)).max()), "max_ref": float(np.abs(ref).max()),
+            "bar": "max(|diff| - 1e-2 |ref|) <= 2e-3"}
+
+
+def time_small_compress(wl: "Workload", reps: int = 50) -> float:
+    """us per launch of the decode step's own compression: one new token per sequence (batch x KV heads items)."""
+    from turboquant.kernels.paged import compress_and_scatter
+    dev = wl.device
+    k = torch.randn(wl.batch, wl.hkv, 128, device=dev, dtype=torch.float16)
+    v = torch.randn(wl.batch, wl.hkv, 128, device=dev, dtype=torch.float16)
+    last = (wl.lens - 1).long()
+    slots = (wl.block_tables.cpu()[torch.arange(wl.batch), (last // 16)].long() * 16 + last % 16).to(dev)
+    for _ in range(3):
+        compress_and_scatter(k, v, wl.caches[0], slots, wl.books, wl.block_size)
+    torch.cuda.synchronize()
+    # captured in a CUDA graph like the e2e step, so that the figure is the kernel, not Python launch overhead
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            compress_and_scatter(k, v, wl.caches[0], slots, wl.books, wl.block_size)
+    graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def time_bulk_compress(fmt_name: str, tokens: int, hkv: int, device, reps: int = 3):
+    """GB/s of compress-and-scatter for `tokens` new tokens x hkv KV heads of fp16 K/V into a paged cache
+    (bytes = fp16 K + V read, packed pages written)."""
+    from turboquant.kernels.paged import CacheFormat, Codebooks, allocate_cache, compress_and_scatter
+    fmt = CacheFormat.named(fmt_name)
+    books = Codebooks(fmt, device)
+    nb = tokens // 16
+    cache = allocate_cache(nb, 16, hkv, fmt, device)
+    g = torch.Generator(device=device).manual_seed(5)
+    K = torch.randn(tokens, hkv, 128, generator=g, device=device, dtype=torch.float16)
+    V = torch.randn(tokens, hkv, 128, generator=g, device=device, dtype=torch.float16)
+    K[..., OUTLIER_CHANNELS] *= 10
+    V[..., OUTLIER_CHANNELS] *= 10
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(6)).to(device)
+    slots = (perm.repeat_interleave(16) * 16 + torch.arange(tokens, device=device) % 16)
+    compress_and_scatter(K, V, cache, slots, books, 16)
+    ms = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        compress_and_scatter(K, V, cache, slots, books, 16)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    nbytes = tokens * hkv * (2 * 128 * 2 + fmt.page_bytes / 16)
+    del K, V, cache
+    return nbytes / (min(ms) / 1e3) / 1e9, min(ms) * 1e3
+
+
+def measure_other_workloads(device, peak: float, steps: int, warmup: int) -> dict:
+    """The other single-GPU workloads, two layers each, measured in the same run (device-resident inputs, CUDA
+    events, one CUDA graph per step): us/layer, GB/s of packed bytes, fraction of the measured peak."""
+    res = {}
+    for name in ("cfg4", "cfg4s", "cfg5"):
+        wl = Workload(name, 0, 1, device, 2)
+        wl.build_caches()
+        torch.cuda.synchronize()
+        ms, skip, _ = time_device_steps(wl, steps, warmup, lambda: None)
+        sec_layer = ms / 1e3 / (steps * wl.layers)
+        gbs = wl.tok_heads_total * wl.bytes_per_tok_head / sec_layer / 1e9
+        comp = wl.compress_ms[-1]
+        row = {"workload": wl.spec["desc"], "layers": wl.layers, "us_per_layer": sec_layer * 1e6, "GBps": gbs,
+               "frac_of_peak": gbs / peak, "pct_of_8TBps": 100 * gbs / 8000.0,
+               "tokens": int(wl.lens.sum()), "compress_GBps": wl.compress_bytes / (comp / 1e3) / 1e9}
+        if skip is not None:
+            row["sparse_v"] = skip
+        res[name] = row
+        del wl
+        torch.cuda.empty_cache()
+    gbs, us = time_bulk_compress("turbo2", 1 << 20, 8, device)
+    res["cfg5_compress_1M_tokens"] = {"workload": "turbo2 compress-and-scatter of 1 048 576 new tokens x 8 KV heads (fp16 K/V)",
+                                      "us": us, "GBps": gbs, "frac_of_peak": gbs / peak, "pct_of_8TBps": 100 * gbs / 8000.0}
+    return res
+
+
+
 def cpu_oracle_sample(fmt_name: str, budget_s: float, threads: int):
     """Time the CPU oracle (numpy restatement of the reference's path) on a bounded sample of the workload:
     whole (sequence, KV-head group) items of 8192 tokens x 8 query heads, compress + decode, as many as fit the
@@ -392,6 +501,13 @@ def cpu_oracle_sample(fmt_name: str, budget_s: float, threads: int):
     from concurrent.futures import ThreadPoolExecutor
     from oracle import tq_oracle as O
     from turboquant.kernels.paged import CacheFormat
+    # One BLAS thread per Python worker: `threads` workers each running an all-core BLAS pool oversubscribe
+    # the host several times over (the same code measured 10x slower that way).
+    try:
+        from threadpoolctl import threadpool_limits
+        blas_guard = threadpool_limits(limits=1)
+    except Exception:                               # threadpoolctl missing: the pools stay as the environment set them
+        blas_guard = None
     fmt = CacheFormat.named(fmt_name)
     L, G = 8192, 8
     kc, kb = O.make_codebook(128, fmt.k_bits)
@@ -436,7 +552,32 @@ def cpu_oracle_sample(fmt_name: str, budget_s: float, threads: int):
             t_dec += time.perf_counter() - t0
             n_dec += len(comp)
     bytes_dec = n_dec * L * fmt.page_bytes / 16
+    if blas_guard is not None:
+        blas_guard.restore_original_limits()
     return bytes_dec / t_dec / 1e9, n_dec, t_dec, 2 * L * threads / t_comp
+
+
+def config_dict(workload: str, layers: int, gpus: int) -> dict:
+    """The workload description both arms print (identical for the same command-line arguments)."""
+    w = WORKLOADS[workload]
+    return {"workload": f"{workload}: {w['desc']}", "format": w["fmt"], "layers": layers, "block_size": 16,
+            "parallelism": f"kv-head sharding x{gpus}",
+            "l2": "each layer has its own cache (>= 3.9x the 126 MB L2 per rank at N=1); no explicit flush",
+            "tolerance": "|diff| <= 2e-3 + 1e-2 |ref| vs fp32 oracle (tests/test_gpu_decode.py)"}
+
+
+def traffic_from_profile(workload: str, world: int):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary of this exact shape
+    (a line `traffic_bytes_per_launch: N` in profiles/decode_partial_turbo3_cfg3.md); None for other shapes."""
+    if workload != "cfg3" or world != 1:
+        return None
+    import re
+    try:
+        with open(os.path.join(ROOT, "profiles", "decode_partial_turbo3_cfg3.md")) as fh:
+            m = re.search(r"traffic_bytes_per_launch:\s*(\d+)", fh.read())
+        return int(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 def load_peak():
@@ -460,18 +601,15 @@ def run_reference_arm(args, rank: int):
         if i >= args.warmup:
             vals.append((gbs, n, secs, vps))
     gbs = statistics.mean(v[0] for v in vals)
-    sample = (f"per step: {vals[0][1]} (sequence, KV-head group) items of 8192 tokens x 8 query heads, "
-              f"{w['fmt']} decode over unpacked oracle fields, {threads} threads")
+    sample = (f"host cores, no GPU; per step a bounded sample of the workload: {vals[0][1]} (sequence, KV-head group) "
+              f"items of 8192 tokens x 8 query heads, {w['fmt']} decode over unpacked oracle fields, {threads} "
+              f"Python threads with one BLAS thread each")
     line = {"impl": "reference", "metric": "tq_decode_attn_hbm_GBps", "value": gbs, "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * statistics.mean(v[2] for v in vals), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            # the same workload as the GPU arm (its config keys); what one CPU step covers is in cpu_baseline.sample
-            "config": {"workload": f"{args.workload}: {w['desc']}", "format": w["fmt"],
-                       "layers": args.layers or w["layers"], "block_size": 16,
-                       "parallelism": f"kv-head sharding x{args.gpus}",
-                       "l2": "host cores: bounded sample of the workload per step, no GPU",
-                       "tolerance": "|diff| <= 2e-3 + 1e-2 |ref| vs fp32 oracle (tests/test_gpu_decode.py)"},
+            # the same workload as the GPU arm (same config dict); what one CPU step covers is in cpu_baseline.sample
+            "config": config_dict(args.workload, args.layers or w["layers"], args.gpus),
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample,
                              "compress_vectors_per_s": statistics.mean(v[3] for v in vals)},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -489,6 +627,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the other workloads' rows (single GPU only)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200" and not args.layers:
         args.warmup = 3
@@ -561,10 +700,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {wl.spec['desc']}", "format": wl.spec["fmt"],
-                       "layers": layers, "block_size": 16, "parallelism": f"kv-head sharding x{world}",
-                       "l2": "each layer has its own cache (>= 3.9x the 126 MB L2 per rank at N=1); no explicit flush",
-                       "tolerance": "|diff| <= 2e-3 + 1e-2 |ref| vs fp32 oracle (tests/test_gpu_decode.py)"},
+            "config": config_dict(args.workload, layers, world),
             "us_per_layer": sec_per_layer * 1e6,
             "tokens_per_s": wl.batch / (sec_per_layer * layers),
             "pct_of_8TBps_per_gpu": 100 * achieved_rank / 8000.0,
@@ -574,9 +710,9 @@ def main():
                          "how": "CUDA events around compress_and_scatter of each layer's fp16 K+V (fresh inputs)"},
             "roofline": {"bound": "hbm", "achieved": achieved_rank, "peak": peak, "unit": "GB/s",
                          "frac": achieved_rank / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape
-                         # (ncu capture summarised in profiles/decode_partial_turbo3_cfg3.md); other shapes: not captured
-                         "traffic": 505980416 if (args.workload == "cfg3" and world == 1) else None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this exact shape, from the
+                         # committed ncu summary; other shapes were not captured
+                         "traffic": traffic_from_profile(args.workload, world),
                          "peak_source": peak_src,
                          "kernel": "decode_partial_kernel (+ merge) per layer per GPU",
                          "algorithmic_bytes_per_launch": bytes_layer_rank},
@@ -595,6 +731,15 @@ def main():
                                    "streams; launched as " + e2e_how}
         if gather_us is not None:
             line["output_all_gather_us"] = gather_us
+        line["parity"] = parity_slice(wl, outs, time_device_steps.last_queries)
+        line["compress"]["decode_step_launch_us"] = time_small_compress(wl)
+        line["compress"]["decode_step_launch_what"] = (f"one new token per sequence: {wl.batch} x {wl.hkv} items per launch "
+                                                       "(the compression inside the e2e step)")
+        if world == 1 and not args.no_others and not args.layers:
+            del outs
+            wl.caches.clear()
+            torch.cuda.empty_cache()
+            line["other_workloads"] = measure_other_workloads(dev, peak, max(2, min(args.steps, 3)), 3)
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
             gbs, n, secs, vps = cpu_oracle_sample(wl.spec["fmt"], budget_s=10.0, threads=threads)

@@ -161,7 +161,7 @@ def test_impl_rejects_extends_and_protected_layers(impl):
     eng.step([("a", 20)])
     with pytest.raises(NotImplementedError):
         eng.step([("a", 5)])                       # five more tokens over cached context: an extend
-    eng2 = _Engine(impl)
+    eng2 = _Engine(B.TurboQuantB200Impl(HQ, 128, SCALE, HKV))      # an implementation object belongs to one layer
     eng2.layer = SimpleNamespace(layer_name="model.layers.0.self_attn.attn")      # first of 40 layers: protected
     with pytest.raises(NotImplementedError):
         eng2.step([("x", 8)])
