@@ -20,6 +20,8 @@
 // turboquant/kernels/packed_attention.py:150-196,273-284, paging and GQA head
 // mapping of turboquant/kernels/sparse_v.py:39-48,70-71, skip rule of
 // sparse_v.py:108-123,149.
+#include <cstdlib>
+
 #include "tq_common.cuh"
 
 namespace tq {
@@ -726,8 +728,29 @@ int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     return launch_chained(kern, grid, dim3(kThreads), smem, stream, p) == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
+}  // namespace
+}  // namespace tq
+
+#include "tq_decode_umma.cuh"
+
+namespace tq {
+namespace {
+
+// TQ_B200_DECODE_PATH=mma keeps every format on the mma.sync kernel (for A/B measurements); read once.
+bool umma_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("TQ_B200_DECODE_PATH");
+        return !(v && v[0] == 'm' && v[1] == 'm' && v[2] == 'a');
+    }();
+    return on;
+}
+
 template <int KB, int VB>
 int dispatch_flags(const DecodeParams& p, bool qjl, bool sparse, dim3 grid, cudaStream_t stream) {
+    if constexpr (KB <= 3 && VB <= 3) {
+        // 2- and 3-bit codebooks without the Sparse-V skip: tensor-memory kernel
+        if (!sparse && umma_enabled()) return qjl ? launch_umma<KB, VB, true>(p, grid, stream) : launch_umma<KB, VB, false>(p, grid, stream);
+    }
     if (qjl) return sparse ? launch_partial<KB, VB, true, true>(p, grid, stream) : launch_partial<KB, VB, true, false>(p, grid, stream);
     return sparse ? launch_partial<KB, VB, false, true>(p, grid, stream) : launch_partial<KB, VB, false, false>(p, grid, stream);
 }
