@@ -257,6 +257,9 @@ class Workload:
 # ------------------------------------------------------------------------------------------------
 # Timed loops
 # ------------------------------------------------------------------------------------------------
+DECODE_FLAGS = 0      # set from --decode-kernel: IO_TCGEN05 selects the tensor-memory variant of the decode kernel
+
+
 def decode_layers(wl: Workload, q_dev: torch.Tensor, outs: torch.Tensor, stats=None):
     """One step: one decode launch pair (partial + merge) per layer, device-resident inputs."""
     from turboquant.kernels import _native
@@ -265,7 +268,7 @@ def decode_layers(wl: Workload, q_dev: torch.Tensor, outs: torch.Tensor, stats=N
     for layer in range(wl.layers):
         _native._decode_paged_impl(outs[layer], q_dev[layer], None, wl.caches[layer], wl.block_tables, wl.seq_lens,
                                    wl.books.kc, wl.books.vc, sm, cs, wl.sparse, wl.block_size, f.k_bits, f.v_bits,
-                                   f.use_qjl, 0, skip_stats=stats)
+                                   f.use_qjl, 0, skip_stats=stats, io_flags=DECODE_FLAGS)
 
 
 def time_device_steps(wl: Workload, steps: int, warmup: int, dist_barrier):
@@ -628,10 +631,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the other workloads' rows (single GPU only)")
+    ap.add_argument("--decode-kernel", default="default", choices=["default", "tcgen05"],
+                    help="tcgen05: time the opt-in tensor-memory variant in the device-resident leg (value / roofline)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200" and not args.layers:
         args.warmup = 3
 
+    if args.decode_kernel == "tcgen05":
+        global DECODE_FLAGS
+        from turboquant.kernels import _native
+        DECODE_FLAGS = _native.IO_TCGEN05
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

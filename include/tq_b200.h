@@ -40,6 +40,9 @@ typedef struct CUstream_st* tq_stream_t; /* same type as cudaStream_t */
 #define TQ_IO_ROTATE_Q 0x100     /* q_rot is given in ORIGINAL space: the kernel rotates it (q' = q H) while loading;
                                     q_proj must be NULL */
 #define TQ_IO_DEROTATE_OUT 0x200 /* write out in original space (out H), as the reference's rotate_output does */
+#define TQ_IO_TCGEN05 0x400      /* run the tensor-memory (tcgen05) variant of the decode kernel where it exists: 2- and
+                                    3-bit codebooks without Sparse-V; other formats ignore the flag.  Slower than the
+                                    default kernel on this hardware and held to the same output tolerance. */
 
 /* Bits set by kernels in the optional device-side status word. */
 #define TQ_STATUS_BAD_BLOCK 1 /* a block-table entry was outside [0, num_blocks) and was clamped */

@@ -20,8 +20,6 @@
 // turboquant/kernels/packed_attention.py:150-196,273-284, paging and GQA head
 // mapping of turboquant/kernels/sparse_v.py:39-48,70-71, skip rule of
 // sparse_v.py:108-123,149.
-#include <cstdlib>
-
 #include "tq_common.cuh"
 
 namespace tq {
@@ -103,6 +101,7 @@ struct DecodeParams {
     int share_tables;        // K and V use the same codebook: one pair table serves both
     int rotate_q;            // the query is in original space: rotate it (fast WHT) while loading
     int derotate_out;        // write the output in original space
+    int use_tcgen05;         // TQ_IO_TCGEN05 was given
 };
 
 // ---------------------------------------------------------------------------------
@@ -736,20 +735,11 @@ int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
 namespace tq {
 namespace {
 
-// TQ_B200_DECODE_PATH=mma keeps every format on the mma.sync kernel (for A/B measurements); read once.
-bool umma_enabled() {
-    static const bool on = [] {
-        const char* v = getenv("TQ_B200_DECODE_PATH");
-        return !(v && v[0] == 'm' && v[1] == 'm' && v[2] == 'a');
-    }();
-    return on;
-}
-
 template <int KB, int VB>
 int dispatch_flags(const DecodeParams& p, bool qjl, bool sparse, dim3 grid, cudaStream_t stream) {
     if constexpr (KB <= 3 && VB <= 3) {
-        // 2- and 3-bit codebooks without the Sparse-V skip: tensor-memory kernel
-        if (!sparse && umma_enabled()) return qjl ? launch_umma<KB, VB, true>(p, grid, stream) : launch_umma<KB, VB, false>(p, grid, stream);
+        // on request (TQ_IO_TCGEN05): the tensor-memory kernel, for 2- and 3-bit codebooks without the Sparse-V skip
+        if (!sparse && p.use_tcgen05) return qjl ? launch_umma<KB, VB, true>(p, grid, stream) : launch_umma<KB, VB, false>(p, grid, stream);
     }
     if (qjl) return sparse ? launch_partial<KB, VB, true, true>(p, grid, stream) : launch_partial<KB, VB, true, false>(p, grid, stream);
     return sparse ? launch_partial<KB, VB, false, true>(p, grid, stream) : launch_partial<KB, VB, false, false>(p, grid, stream);
@@ -830,6 +820,7 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_pages_per_seq <= 0 || num_blocks <= 0) return TQ_ERR_ARG;
     if (num_q_heads % num_kv_heads) return TQ_ERR_ARG;
     const int rotate_q = (io_dtype & TQ_IO_ROTATE_Q) ? 1 : 0, derotate_out = (io_dtype & TQ_IO_DEROTATE_OUT) ? 1 : 0;
+    const int use_tcgen05 = (io_dtype & TQ_IO_TCGEN05) ? 1 : 0;
     io_dtype &= 0xff;
     if (io_dtype != TQ_DTYPE_F16 && io_dtype != TQ_DTYPE_BF16) return TQ_ERR_UNSUPPORTED;
     if (rotate_q && q_proj) return TQ_ERR_ARG;   // S q' cannot be derived from an unrotated query
@@ -878,6 +869,7 @@ extern "C" int tq_decode_paged(void* out, const void* q_rot, const void* q_proj,
     p.io_dtype = io_dtype;
     p.rotate_q = rotate_q;
     p.derotate_out = derotate_out;
+    p.use_tcgen05 = use_tcgen05;
     p.share_tables = (k_bits == v_bits && k_centroids == v_centroids) ? 1 : 0;
 
     const dim3 grid(max_chunks, num_kv_heads * p.ngroups, num_seqs);

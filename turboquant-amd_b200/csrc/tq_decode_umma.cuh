@@ -58,7 +58,7 @@ struct UmSmem {
     static constexpr int kQP = 4096;                // B operand of the sign product, 2 KB
     static constexpr int kP = 6144;                 // [2] x 2 KB
     static constexpr int kV = 10240;                // [2] x 2 planes x 16 KB
-    static constexpr int kRing = 10240 + 65536;     // [kUmStages] x 8 x page stride (two CTAs of ~104 KB fit one SM)
+    static constexpr int kRing = 10240 + 65536;     // [kUmStages] x 8 x page stride (two CTAs of ~104 KB fit one SM) (two CTAs of ~104 KB fit one SM)
 };
 
 enum UmBar { kFull = 0, kEmpty = 3, kKReady = 6, kSDone = 8, kSFree = 9, kPReady = 10, kVReady = 12, kPVDone = 14, kNumBars = 16 };
@@ -151,24 +151,52 @@ __device__ __forceinline__ float lds_half(uint32_t addr) {
     return __half2float(__ushort_as_half(h));
 }
 
-// Byte tables of one codebook: c[i] * S = hi[i] + lo[i] with both in e4m3; S is the power of two that puts the
-// largest centroid in [128, 256).  Returns 1 / S.
+// Byte tables of one codebook: c[i] * S = hi[i] + lo[i] with both in e4m3.  Sixteen lanes (lane & 15 = candidate j) try
+// S = 2^e (1 + j / 16), with 2^e the power of two that puts the largest centroid in [64, 128), and the candidate whose
+// worst centroid is represented best wins (a codebook has few distinct magnitudes, so some scale puts all of them close
+// to byte pairs); the winner writes the tables.  Every lane of the half-warp returns 1 / S.
 template <int BITS>
-__device__ __forceinline__ float build_byte_tables(const float* __restrict__ c, uint8_t* hi, uint8_t* lo) {
-    float mx = 0.f;
-    for (int i = 0; i < (1 << BITS); ++i) mx = fmaxf(mx, fabsf(__ldg(c + i)));
-    int e = 0;
-    if (mx > 0.f && mx < __uint_as_float(0x7f800000u)) e = 134 - static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu);   // 2^e * mx in [128, 256)
-    e = max(-100, min(100, e));
-    const float S = __uint_as_float(static_cast<uint32_t>(127 + e) << 23), invS = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    for (int i = 0; i < 8; ++i) {
-        const float v = i < (1 << BITS) ? __ldg(c + i) * S : 0.f;
-        const uint32_t h = cvt_e4m3x2(0.f, v) & 0xffu;
-        const uint32_t l = cvt_e4m3x2(0.f, v - e4m3_to_float(h)) & 0xffu;
-        hi[i] = static_cast<uint8_t>(h);
-        lo[i] = static_cast<uint8_t>(l);
+__device__ __forceinline__ float build_byte_tables(const float* __restrict__ c, uint8_t* hi, uint8_t* lo, int lane) {
+    float cv[1 << BITS], mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < (1 << BITS); ++i) {
+        cv[i] = __ldg(c + i);
+        mx = fmaxf(mx, fabsf(cv[i]));
     }
-    return invS;
+    int e = 0;
+    if (mx > 0.f && mx < __uint_as_float(0x7f800000u)) e = 133 - static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu);   // 2^e * mx in [64, 128)
+    e = max(-100, min(100, e));
+    const int j = lane & 15;
+    const float S = __uint_as_float(static_cast<uint32_t>(127 + e) << 23) * (1.f + static_cast<float>(j) * 0.0625f);
+    uint32_t hb[1 << BITS], lb[1 << BITS];
+    float err = 0.f;
+#pragma unroll
+    for (int i = 0; i < (1 << BITS); ++i) {
+        const float v = cv[i] * S;
+        hb[i] = cvt_e4m3x2(0.f, v) & 0xffu;
+        const float h = e4m3_to_float(hb[i]);
+        lb[i] = cvt_e4m3x2(0.f, v - h) & 0xffu;
+        const float rep = h + e4m3_to_float(lb[i]);
+        err = fmaxf(err, fabsf(v - rep) / fmaxf(fabsf(v), 1e-30f));
+    }
+    // argmin over the 16 candidates of this half-warp (ties: the smaller j)
+    float best = err;
+    int who = j;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+        const float oe = __shfl_xor_sync(0xffffffffu, best, o);
+        const int ow = __shfl_xor_sync(0xffffffffu, who, o);
+        if (oe < best || (oe == best && ow < who)) { best = oe; who = ow; }
+    }
+    if (j == who) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            hi[i] = i < (1 << BITS) ? static_cast<uint8_t>(hb[i < (1 << BITS) ? i : 0]) : 0;
+            lo[i] = i < (1 << BITS) ? static_cast<uint8_t>(lb[i < (1 << BITS) ? i : 0]) : 0;
+        }
+    }
+    const float Sw = __uint_as_float(static_cast<uint32_t>(127 + e) << 23) * (1.f + static_cast<float>(who) * 0.0625f);
+    return 1.f / Sw;
 }
 
 #ifdef TQ_UM_TRACE
@@ -243,6 +271,8 @@ __global__ void __launch_bounds__(kUmThreads, 2) decode_umma_kernel(const Decode
         }
         mbar_init(bars + kSDone, 1);                  // tcgen05.commit
         mbar_init(bars + kSFree, 4);                  // key warps have read the score accumulators
+        mbar_init(bars + kSDone, 1);                  // tcgen05.commit
+        mbar_init(bars + kSFree, 4);                  // key warps have read the score accumulators
         fence_barrier_init();
     }
     if (warp == 9) {
@@ -250,13 +280,11 @@ __global__ void __launch_bounds__(kUmThreads, 2) decode_umma_kernel(const Decode
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (warp == 8) {
-        if (lane == 0) {
-            const float inv_sk = build_byte_tables<KB>(p.kc, smem + UmSmem::kTab, smem + UmSmem::kTab + 8);
-            scal[0] = inv_sk;                       // completed below once the query scale is known
-        } else if (lane == 1) {
-            const float inv_sv = build_byte_tables<VB>(p.vc, smem + UmSmem::kTab + 16, smem + UmSmem::kTab + 24);
-            scal[2] = inv_sv * (1.f / kWScale);
-        }
+        // lanes 0-15: key codebook, lanes 16-31: value codebook
+        const float inv_s = lane < 16 ? build_byte_tables<KB>(p.kc, smem + UmSmem::kTab, smem + UmSmem::kTab + 8, lane)
+                                      : build_byte_tables<VB>(p.vc, smem + UmSmem::kTab + 16, smem + UmSmem::kTab + 24, lane);
+        if (lane == 0) scal[0] = inv_s;             // completed below once the query scale is known
+        if (lane == 16) scal[2] = inv_s * (1.f / kWScale);
     }
     if (warp == 0) {
         // Query rows of the group (lane = (row gid, quarter tig) as in the mma.sync kernel), split q = q1 + q2 in e4m3
@@ -520,23 +548,20 @@ __global__ void __launch_bounds__(kUmThreads, 2) decode_umma_kernel(const Decode
             float w1v[8], w2v[8];
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
-                const float wv = ex2(sc[h] - mt[h]);                       // <= 1 (up to the 1/1024 step)
-                l_acc[h] = fmaf(l_acc[h], al[h], wv * rvn * be[h]);
-                const float ws = wv * kWScale;
+                const float ws = ex2(sc[h] - mt[h]) * kWScale;              // weight <= 1 (up to the 1/1024 step), times 256
                 w1v[h] = __uint_as_float(__float_as_uint(ws) & 0xFFF00000u);   // 4 significant bits: exact in e4m3 when in range
-                w2v[h] = ws - w1v[h];
+                w2v[h] = __uint_as_float(__float_as_uint(ws - w1v[h]) & 0xFFF00000u);
+                // the denominator sums the weight the value product really uses (w1 + w2), so a lone token comes out exactly
+                l_acc[h] = fmaf(l_acc[h], al[h], (w1v[h] + w2v[h]) * (rvn * (1.f / kWScale)) * be[h]);
             }
-            // the weights go to the operand as e4m3 after rounding; the denominator above uses the unrounded weight,
-            // the difference is below 2^-8 per token
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 b1[j] = cvt_e4m3x2(w1v[2 * j + 1], w1v[2 * j]);
                 b2[j] = cvt_e4m3x2(w2v[2 * j + 1], w2v[2 * j]);
             }
-            // the P buffer of this parity was last read by the value product two tiles ago
-            UM_TRACE(0, i, 9);
-            if (i >= 2 && !mbar_wait_bounded(bars + kPVDone + b, ((i - 2) >> 1) & 1)) { timed_out = true; break; }
-            UM_TRACE(0, i, 10);
+            // The P buffer of this parity was last read by the value product two tiles ago.  The MMA thread issued that
+            // product before the score product of this tile, and tcgen05 operations of one thread complete in order:
+            // seeing S(i) done (above) already says that PV(i - 2) is done.
             sts_u128(sbase + UmSmem::kP + b * 2048 + tid * 16, b1[0] | (b1[1] << 16), b1[2] | (b1[3] << 16),
                      b2[0] | (b2[1] << 16), b2[2] | (b2[3] << 16));
             fence_proxy_async();
@@ -670,7 +695,7 @@ template <int KB, int VB, bool QJL>
 int launch_umma(const DecodeParams& p, dim3 grid, cudaStream_t stream) {
     constexpr int PAGE = page_bytes(KB, VB, QJL ? 1 : 0);
     constexpr size_t smem = UmSmem::kRing + static_cast<size_t>(kUmStages) * kUmTilePages * um_page_stride(PAGE);
-    static_assert(smem <= 227 * 1024, "shared memory budget");
+    static_assert(smem <= 113 * 1024, "two CTAs per SM");
     auto kern = decode_umma_kernel<KB, VB, QJL>;
     static bool configured[64] = {};
     int dev = 0;

@@ -26,6 +26,7 @@ STATUS_TIMEOUT = 2
 STATUS_BAD_SLOT = 4
 IO_ROTATE_Q = 0x100        # q is in original space: rotate it inside the decode kernel
 IO_DEROTATE_OUT = 0x200    # write the decode output in original space
+IO_TCGEN05 = 0x400         # tensor-memory variant of the decode kernel (2- / 3-bit codebooks, no Sparse-V)
 
 _lib: Optional[ctypes.CDLL] = None
 

@@ -94,7 +94,7 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
                            q_proj: Optional[torch.Tensor] = None, rotate_q: bool = False,
                            derotate_out: bool = False, chunk_pages: int = 0,
                            out: Optional[torch.Tensor] = None, skip_stats: Optional[torch.Tensor] = None,
-                           max_seq_len: int = 0, static_scratch: bool = False) -> torch.Tensor:
+                           max_seq_len: int = 0, static_scratch: bool = False, tcgen05: bool = False) -> torch.Tensor:
     """One decode step over the packed paged cache.
 
     q [num_seqs, Hq, 128] fp16/bf16.  With rotate_q the query is first taken to
@@ -106,6 +106,7 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
     max_seq_len: the longest sequence of the step when the host knows it (a serving engine does); the launch is
     then sized for it rather than for the width of block_tables.  static_scratch: keep the split-K partials in
     the library's fixed 16 MiB device array instead of a torch workspace (no allocation; larger problems raise).
+    tcgen05: run the tensor-memory variant of the kernel (2- and 3-bit codebooks without Sparse-V; others ignore it).
     """
     fmt = books.fmt
     if sm_scale is None:
@@ -116,6 +117,8 @@ def paged_decode_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: t
     # Both rotations run inside the decode kernels (query rotated while its fragments are loaded, output
     # de-rotated where it is normalised); only a separate q_proj forces the query rotation to be its own pass.
     flags = _native.IO_DEROTATE_OUT if derotate_out else 0
+    if tcgen05:
+        flags |= _native.IO_TCGEN05
     if rotate_q and q_proj is None:
         flags |= _native.IO_ROTATE_Q
         q_in = q
