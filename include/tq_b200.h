@@ -45,6 +45,8 @@ typedef struct CUstream_st* tq_stream_t; /* same type as cudaStream_t */
                                     default kernel on this hardware and held to the same output tolerance. */
 
 /* Bits set by kernels in the optional device-side status word. */
+#define TQ_COMPRESS_TCGEN05 2 /* flag in tq_compress_paged's `prerotated` argument, see there */
+
 #define TQ_STATUS_BAD_BLOCK 1 /* a block-table entry was outside [0, num_blocks) and was clamped */
 #define TQ_STATUS_TIMEOUT 2   /* a bounded wait on an async copy ran out */
 #define TQ_STATUS_BAD_SLOT 4  /* a slot index was >= num_blocks * block_size and was skipped */
@@ -85,7 +87,13 @@ int tq_page_bytes(int k_bits, int v_bits, int use_qjl);
  * slower generic path with the same results.  A vector that contains a NaN or
  * an infinity gets the indices of a zero vector and a non-finite norm.  The
  * first call on a device sets a function attribute (shared-memory size) and
- * should be made before any stream capture. */
+ * should be made before any stream capture.
+ *
+ * prerotated: 0 = rotate here, 1 = the rows are already rotated; OR-ed with
+ * TQ_COMPRESS_TCGEN05 the rotation of fp16 / bf16 rows of a large launch runs as
+ * one 128 x 128 x 128 tcgen05 product per 128 rows with one thread per vector
+ * afterwards (an opt-in variant: same results within the rotation allowance,
+ * about 15 % slower than the default kernel on this hardware). */
 int tq_compress_paged(const void* key, const void* value, int in_dtype,
                       int64_t k_stride_token, int64_t k_stride_head,
                       int64_t v_stride_token, int64_t v_stride_head,

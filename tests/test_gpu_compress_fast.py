@@ -35,7 +35,7 @@ def _fp16_ulps(got_h: torch.Tensor, want_f32: np.ndarray) -> int:
     return int((a - b).abs().max())
 
 
-def _run(key, val, fmt, books, block_size=16, prerotated=False, slots=None, seed=0):
+def _run(key, val, fmt, books, block_size=16, prerotated=False, slots=None, seed=0, tcgen05=False):
     T, Hkv = key.shape[:2]
     assert T * Hkv > FAST_MIN_ITEMS
     nb = (T + block_size - 1) // block_size + 3
@@ -43,7 +43,8 @@ def _run(key, val, fmt, books, block_size=16, prerotated=False, slots=None, seed
         slots = torch.randperm(nb * block_size, generator=torch.Generator().manual_seed(seed))[:T]
     cache = allocate_cache(nb, block_size, Hkv, fmt, DEV)
     cache.fill_(0x5A)
-    compress_and_scatter(key.to(DEV), val.to(DEV), cache, slots.to(DEV), books, block_size, prerotated=prerotated)
+    compress_and_scatter(key.to(DEV), val.to(DEV), cache, slots.to(DEV), books, block_size, prerotated=prerotated,
+                         tcgen05=tcgen05)
     status = _native.read_status(DEV)
     f = paged_layout.unpack_cache(cache.cpu(), block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl)
     blk, off = slots // block_size, slots % block_size
@@ -58,15 +59,17 @@ def _oracle(key, val, fmt, books, H):
     return ok, ov
 
 
+@pytest.mark.parametrize("tcgen05", [False, True])
 @pytest.mark.parametrize("fmt_name", ["turbo2", "turbo3", "turbo4"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_fast_kernel_tensor_core_rotation_vs_oracle(fmt_name, dtype):
-    """fp16 / bf16 rows rotated on the tensor cores: at most 1e-4 of the coordinates differ from the oracle, never
-    by more than one centroid; norms within one fp16 ulp; the ragged last group stores only live items."""
+def test_fast_kernel_tensor_core_rotation_vs_oracle(fmt_name, dtype, tcgen05):
+    """fp16 / bf16 rows rotated on the tensor cores (mma.sync kernel, and the opt-in tcgen05 kernel with one thread
+    per vector): at most 1e-4 of the coordinates differ from the oracle, never by more than one centroid; norms
+    within one fp16 ulp; the ragged last group stores only live items."""
     fmt = CacheFormat.named(fmt_name)
     books = Codebooks(fmt, DEV)
     key, val = _kv(T_BIG, HKV, dtype, seed=41)
-    got, status, _ = _run(key, val, fmt, books)
+    got, status, _ = _run(key, val, fmt, books, tcgen05=tcgen05)
     assert status == 0
     ok, ov = _oracle(key, val, fmt, books, O.make_wht_matrix(128))
     gk, gv = got["k_idx"].numpy().reshape(-1, 128).astype(int), got["v_idx"].numpy().reshape(-1, 128).astype(int)
@@ -116,15 +119,15 @@ def test_fast_kernel_plain_branch_fp32_rotated(fmt_name):
         assert (got["k_signs"].numpy().reshape(-1, 128) != (ok["signs"] > 0)).mean() <= 1e-4
 
 
-@pytest.mark.parametrize("prerotated", [False, True])
-def test_fast_kernel_tight_codebook_falls_back_inside_the_kernel(prerotated):
-    """Two boundaries inside one 1/64 cell: the persistent kernel itself switches to the binary search."""
+@pytest.mark.parametrize("prerotated,tcgen05", [(False, False), (True, False), (False, True)])
+def test_fast_kernel_tight_codebook_falls_back_inside_the_kernel(prerotated, tcgen05):
+    """Two boundaries inside one 1/64 cell: the persistent kernels themselves switch to the binary search."""
     fmt = CacheFormat.named("turbo3")
     b = torch.tensor([-0.03, -0.02, -0.01, 0.0, 0.01, 0.02, 0.03])
     c = torch.tensor([-0.05, -0.025, -0.015, -0.005, 0.005, 0.015, 0.025, 0.05])
     books = Codebooks(fmt, DEV, k_codebook=(c, b), v_codebook=(c, b))
     key, val = _kv(T_BIG, HKV, torch.float16, seed=53)
-    got, status, _ = _run(key, val, fmt, books, prerotated=prerotated)
+    got, status, _ = _run(key, val, fmt, books, prerotated=prerotated, tcgen05=tcgen05)
     assert status == 0
     ok, ov = _oracle(key, val, fmt, books, None if prerotated else O.make_wht_matrix(128))
     gk, gv = got["k_idx"].numpy().reshape(-1, 128).astype(int), got["v_idx"].numpy().reshape(-1, 128).astype(int)
@@ -139,20 +142,21 @@ def test_fast_kernel_tight_codebook_falls_back_inside_the_kernel(prerotated):
         assert (gs != (ok["signs"] > 0)).mean() <= 1e-3
 
 
-@pytest.mark.parametrize("dtype,prerotated", [(torch.float16, False), (torch.bfloat16, False), (torch.float32, False),
-                                              (torch.float16, True)])
-def test_fast_kernel_nonfinite_rows_only_spoil_themselves(dtype, prerotated):
+@pytest.mark.parametrize("dtype,prerotated,tcgen05", [(torch.float16, False, False), (torch.bfloat16, False, False),
+                                                      (torch.float32, False, False), (torch.float16, True, False),
+                                                      (torch.float16, False, True), (torch.bfloat16, False, True)])
+def test_fast_kernel_nonfinite_rows_only_spoil_themselves(dtype, prerotated, tcgen05):
     """NaN / Inf inside a vector: that vector's norm shows it, every other byte of the cache is unchanged."""
     fmt = CacheFormat.named("turbo3")
     books = Codebooks(fmt, DEV)
     key, val = _kv(T_BIG, HKV, dtype, seed=59)
     slots = torch.randperm((T_BIG // 16 + 4) * 16, generator=torch.Generator().manual_seed(5))[:T_BIG]
-    clean, s0, _ = _run(key, val, fmt, books, prerotated=prerotated, slots=slots)
+    clean, s0, _ = _run(key, val, fmt, books, prerotated=prerotated, slots=slots, tcgen05=tcgen05)
     bad_k, bad_v = key.clone(), val.clone()
     bad_k[3, 1, 17] = float("nan")
     bad_k[1500, 0, 100] = float("inf")
     bad_v[2099, 7, 0] = float("-inf")
-    dirty, s1, _ = _run(bad_k, bad_v, fmt, books, prerotated=prerotated, slots=slots)
+    dirty, s1, _ = _run(bad_k, bad_v, fmt, books, prerotated=prerotated, slots=slots, tcgen05=tcgen05)
     assert s0 == 0 and s1 == 0
     keep_k = torch.ones(T_BIG, HKV, dtype=torch.bool)
     keep_k[3, 1] = keep_k[1500, 0] = False

@@ -234,6 +234,7 @@ struct PagedParams {
     int64_t num_slots;
     int64_t n_items;   // n_tokens * n_kv_heads
     int Hkv, block_size, in_dtype, rotate;
+    int use_tcgen05;       // TQ_COMPRESS_TCGEN05 was given
 };
 
 // Where one (token, head) item goes in the paged cache; live = false when the item is past the end or its
@@ -336,6 +337,7 @@ __device__ __noinline__ void compress_items_generic(const PagedParams& p, int64_
 }  // namespace tq
 
 #include "tq_compress_fast.cuh"
+#include "tq_compress_tc.cuh"
 
 namespace tq {
 namespace {
@@ -535,7 +537,8 @@ extern "C" int tq_compress_paged(const void* key, const void* value, int in_dtyp
     p.Hkv = n_kv_heads;
     p.block_size = block_size;
     p.in_dtype = in_dtype;
-    p.rotate = prerotated ? 0 : 1;
+    p.rotate = (prerotated & 1) ? 0 : 1;
+    p.use_tcgen05 = (prerotated & TQ_COMPRESS_TCGEN05) ? 1 : 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (k_bits) {
         case 2: return launch_paged_v<2>(p, v_bits, use_qjl != 0, st);

@@ -651,12 +651,18 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compress_paged_small_kernel
 constexpr int64_t kSmallLaunchItems = 16384;   // below this the table set-up and the 512-thread CTAs of the fast kernel cost more than they save
 
 template <int KB, int VB, bool QJL>
+int launch_paged_tc(const PagedParams& p, cudaStream_t st);   // tq_compress_tc.cuh
+
+template <int KB, int VB, bool QJL>
 int launch_paged_fast(const PagedParams& p, cudaStream_t st) {
     if (p.n_items <= kSmallLaunchItems) {
         const unsigned grid = static_cast<unsigned>((p.n_items + kItemsPerCta - 1) / kItemsPerCta);
         compress_paged_small_kernel<KB, VB, QJL><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
         return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
     }
+    // on request: fp16 / bf16 rows that still need the rotation go to the tensor-memory kernel (rotation as one
+    // 128 x 128 x 128 product per 128 rows, one thread per vector afterwards)
+    if (p.rotate && p.in_dtype != TQ_DTYPE_F32 && p.use_tcgen05) return launch_paged_tc<KB, VB, QJL>(p, st);
     const int64_t n_groups = (p.n_items + kFastItemsPerCta - 1) / kFastItemsPerCta;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return TQ_ERR_LAUNCH;

@@ -163,8 +163,11 @@ def page_bytes(k_bits: int, v_bits: int, use_qjl: bool) -> int:
     return rc
 
 
+COMPRESS_TCGEN05 = 2       # flag in tq_compress_paged's `prerotated` argument: tensor-memory rotation kernel
+
+
 def _compress_paged_impl(key, value, cache, slot_mapping, kc, kb, vc, vb, block_size, k_bits, v_bits, use_qjl,
-                         prerotated) -> None:
+                         prerotated, tcgen05: bool = False) -> None:
     dev = _require_cuda(key, value, cache, slot_mapping, kc, kb, vc, vb)
     if key.dim() != 3 or key.shape[-1] != 128 or value.shape != key.shape:
         raise ValueError("key/value must be [tokens, kv_heads, 128]")
@@ -189,7 +192,8 @@ def _compress_paged_impl(key, value, cache, slot_mapping, kc, kb, vc, vb, block_
         rc = lib().tq_compress_paged(
             _ptr(key), _ptr(value), _DTYPES[key.dtype], key.stride(0), key.stride(1), value.stride(0), value.stride(1),
             _ptr(cache), cache.shape[0], block_size, _ptr(slot_mapping), _ptr(kc), _ptr(kb), _ptr(vc), _ptr(vb),
-            T, H, k_bits, v_bits, int(use_qjl), int(prerotated), _ptr(status_word(dev)), _stream(dev))
+            T, H, k_bits, v_bits, int(use_qjl), int(bool(prerotated)) | (COMPRESS_TCGEN05 if tcgen05 else 0),
+            _ptr(status_word(dev)), _stream(dev))
     _check(rc, "tq_compress_paged")
 
 

@@ -75,7 +75,7 @@ def allocate_cache(num_blocks: int, block_size: int, num_kv_heads: int, fmt: Cac
 
 
 def compress_and_scatter(key: torch.Tensor, value: torch.Tensor, cache: torch.Tensor, slot_mapping: torch.Tensor,
-                         books: Codebooks, block_size: int, prerotated: bool = False) -> None:
+                         books: Codebooks, block_size: int, prerotated: bool = False, tcgen05: bool = False) -> None:
     """Compress key/value [T, Hkv, 128] and write them at `slot_mapping` (int64 [T]) into the paged cache.
 
     Slot s lands in block s // block_size at offset s % block_size; negative
@@ -84,6 +84,12 @@ def compress_and_scatter(key: torch.Tensor, value: torch.Tensor, cache: torch.Te
     fmt = books.fmt
     if slot_mapping.dtype != torch.int64:
         slot_mapping = slot_mapping.to(torch.int64)
+    if tcgen05:
+        # opt-in variant: rotation of fp16 / bf16 rows as a tcgen05 product (large launches only; otherwise ignored)
+        from turboquant.kernels import _native
+        _native._compress_paged_impl(key, value, cache, slot_mapping.contiguous(), books.kc, books.kb, books.vc, books.vb,
+                                     block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, prerotated, tcgen05=True)
+        return
     torch.ops.tq_b200.compress_paged(key, value, cache, slot_mapping.contiguous(), books.kc, books.kb, books.vc,
                                      books.vb, block_size, fmt.k_bits, fmt.v_bits, fmt.use_qjl, prerotated)
 
