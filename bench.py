@@ -441,6 +441,9 @@ def time_small_compress(wl: "Workload", reps: int = 50) -> float:
     return e0.elapsed_time(e1) * 1e3 / reps
 
 
+TC = False     # time the opt-in tensor-memory rotation kernel in time_bulk_compress
+
+
 def time_bulk_compress(fmt_name: str, tokens: int, hkv: int, device, reps: int = 3):
     """GB/s of compress-and-scatter for `tokens` new tokens x hkv KV heads of fp16 K/V into a paged cache
     (bytes = fp16 K + V read, packed pages written)."""
@@ -456,12 +459,12 @@ def time_bulk_compress(fmt_name: str, tokens: int, hkv: int, device, reps: int =
     V[..., OUTLIER_CHANNELS] *= 10
     perm = torch.randperm(nb, generator=torch.Generator().manual_seed(6)).to(device)
     slots = (perm.repeat_interleave(16) * 16 + torch.arange(tokens, device=device) % 16)
-    compress_and_scatter(K, V, cache, slots, books, 16)
+    compress_and_scatter(K, V, cache, slots, books, 16, tcgen05=TC)
     ms = []
     for _ in range(reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        compress_and_scatter(K, V, cache, slots, books, 16)
+        compress_and_scatter(K, V, cache, slots, books, 16, tcgen05=TC)
         e1.record()
         e1.synchronize()
         ms.append(e0.elapsed_time(e1))

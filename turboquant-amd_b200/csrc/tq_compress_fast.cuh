@@ -190,13 +190,18 @@ struct VecConsts {
 // squared residuals and shifts the sign bits of the two residuals into `sacc` (1 = negative; pairs must come in
 // descending order).  A residual that underflows to -0.0 is the one case that reads as negative here while the
 // reference's (e >= 0) calls it positive.
-template <bool QJL>
+// EXACT: u = y / den correctly rounded (one reciprocal multiply plus two correction FMAs), as the reference's true
+// division; needed where the input is already rotated and the indices must be the reference's bit for bit.  Where the
+// rotation is done here its own rounding already moves u in the last bits, so the kernels that rotate take the plain
+// product y * (1 / den), at most one ulp away: a different index only for u within an ulp of a boundary (~1e-7 of
+// the coordinates, inside the rotation's 1e-4 allowance).
+template <bool QJL, bool EXACT = true>
 __device__ __forceinline__ void quant_pair(f2 y, const VecConsts& vc, f2& rr, uint32_t& sacc, float& kfa, float& kfb) {
     const float kBig = big();
     const f2 q0 = f2mul(y, vc.inv);
     // The cell only needs the quotient to ~1e-6: take it from the first approximation so the lookup starts early.
     const f2 cellf = f2fma(y, vc.inv64, f2dup(kMagic + kCellScale));   // low mantissa bits: round(scale u) + scale
-    const f2 u = f2fma(f2fma(q0, vc.nden, y), vc.inv, q0);       // = y / den, correctly rounded; |u| <= 1
+    const f2 u = EXACT ? f2fma(f2fma(q0, vc.nden, y), vc.inv, q0) : q0;   // y / den (correctly rounded when EXACT); |u| <= 1
     float ua, ub, cfa, cfb;
     f2unpack(u, ua, ub);
     f2unpack(cellf, cfa, cfb);
@@ -460,8 +465,8 @@ __device__ __forceinline__ void compress_row_mma(uint32_t row, bool live, int la
             const int c = 2 * j + nt;   // chunk of dims 4 c .. 4 c + 3
             float k0, k1, k2, k3;
             uint32_t nib = 0u;
-            quant_pair<QJL>(y[2 * j + 1], vc, rr, nib, k2, k3);
-            quant_pair<QJL>(y[2 * j], vc, rr, nib, k0, k1);
+            quant_pair<QJL, false>(y[2 * j + 1], vc, rr, nib, k2, k3);
+            quant_pair<QJL, false>(y[2 * j], vc, rr, nib, k0, k1);
             cv[c] = fmaf(fmaf(fmaf(k3, 16.f, k2), 16.f, k1), 16.f, k0);
             if constexpr (QJL) sg |= nib << (4 * c);
         }

@@ -80,21 +80,27 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 
-// One quarter (32 dims as 16 pairs) of a vector through the table-driven quantizer; rr accumulates the squared
-// residuals of the whole vector.
-template <int BITS, bool QJL, bool ISV>
-__device__ __forceinline__ void quantize_quarter_fast(const f2 (&y)[16], const VecConsts& vc, f2& rr, Packed& out) {
-    float cv[8];
-    uint32_t sg[2] = {0u, 0u};
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Half a quarter (16 dims = chunks 4 h .. 4 h + 3 of the quarter, as 8 pairs) through the table-driven quantizer:
+// fills cv[4 h .. 4 h + 3] and the 16 sign bits sg (1 = negative; the upper half must be done first only in the sense
+// that each half has its own accumulator); rr accumulates the squared residuals of the whole vector.
+template <bool QJL>
+__device__ __forceinline__ void quantize_half_fast(const uint32_t (&d)[16], const VecConsts& vc, f2& rr, float (&cv4)[4], uint32_t& sg) {
+    sg = 0u;
 #pragma unroll
-    for (int c = 7; c >= 0; --c) {
+    for (int c = 3; c >= 0; --c) {
         float k0, k1, k2, k3;
-        quant_pair<QJL>(y[2 * c + 1], vc, rr, sg[c >> 2], k2, k3);
-        quant_pair<QJL>(y[2 * c], vc, rr, sg[c >> 2], k0, k1);
-        cv[c] = fmaf(fmaf(fmaf(k3, 16.f, k2), 16.f, k1), 16.f, k0);
+        quant_pair<QJL, false>(f2pack(__uint_as_float(d[4 * c + 2]), __uint_as_float(d[4 * c + 3])), vc, rr, sg, k2, k3);
+        quant_pair<QJL, false>(f2pack(__uint_as_float(d[4 * c]), __uint_as_float(d[4 * c + 1])), vc, rr, sg, k0, k1);
+        cv4[c] = fmaf(fmaf(fmaf(k3, 16.f, k2), 16.f, k1), 16.f, k0);
     }
-    assemble_indices<BITS, ISV>(cv, out);
-    out.signs = QJL ? ~prmt(sg[0], sg[1], 0x5410) : 0u;
 }
 
 template <int KB, int VB, bool QJL>
@@ -207,19 +213,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) compress_paged_tc_kernel(const 
             // the staging buffer is free again: next tile's copies fly while this one is quantized
             if (tile + tile_step < n_tiles) stage_tile(tile + tile_step);
 
-            // ---- pass 1: squared norm of the rotated vector ------------------------------------------------------
+            // ---- pass 1: squared norm of the rotated vector (16 columns at a time, next load in flight) -----------
             f2 acc0 = f2dup(0.f), acc1 = f2dup(0.f);
+            {
+                uint32_t da[16], db[16];
+                auto sum16 = [&](const uint32_t (&d)[16]) {
 #pragma unroll
-            for (int qt = 0; qt < 4; ++qt) {
-                uint32_t d[32];
-                tc_ld32(dcol + qt * 32, d);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const f2 a = f2pack(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1]));
-                    const f2 b = f2pack(__uint_as_float(d[2 * i + 2]), __uint_as_float(d[2 * i + 3]));
-                    acc0 = f2fma(a, a, acc0);
-                    acc1 = f2fma(b, b, acc1);
+                    for (int i = 0; i < 16; i += 4) {
+                        const f2 a = f2pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1]));
+                        const f2 b = f2pack(__uint_as_float(d[i + 2]), __uint_as_float(d[i + 3]));
+                        acc0 = f2fma(a, a, acc0);
+                        acc1 = f2fma(b, b, acc1);
+                    }
+                };
+                tc_ld16(dcol, da);
+#pragma unroll 1
+                for (int h = 0; h < 8; h += 2) {
+                    tc_wait_ld();
+                    tc_ld16(dcol + (h + 1) * 16, db);
+                    sum16(da);
+                    tc_wait_ld();
+                    if (h + 2 < 8) tc_ld16(dcol + (h + 2) * 16, da);
+                    sum16(db);
                 }
             }
             float s0, s1, s2, s3;
@@ -230,22 +245,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) compress_paged_tc_kernel(const 
             if (__any_sync(0xffffffffu, !finite)) {
                 // NaN or overflow somewhere in a vector: its row of the product is replaced by zeros so that the table
                 // look-ups stay in range (the stored norm still shows the bad value); rare, so a branch of its own
-                uint32_t z[32];
+#pragma unroll 1
+                for (int h = 0; h < 8; ++h) {
+                    uint32_t d[16];
+                    tc_ld16(dcol + h * 16, d);
+                    tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) z[i] = 0u;
-#pragma unroll
-                for (int qt = 0; qt < 4; ++qt) {
-                    uint32_t d[32];
-                    tc_ld32(dcol + qt * 32, d);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) d[i] = finite ? d[i] : z[i];
-                    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-                                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-                                 ::"r"(dcol + qt * 32), "r"(d[0]), "r"(d[1]), "r"(d[2]), "r"(d[3]), "r"(d[4]), "r"(d[5]), "r"(d[6]), "r"(d[7]),
-                                   "r"(d[8]), "r"(d[9]), "r"(d[10]), "r"(d[11]), "r"(d[12]), "r"(d[13]), "r"(d[14]), "r"(d[15]),
-                                   "r"(d[16]), "r"(d[17]), "r"(d[18]), "r"(d[19]), "r"(d[20]), "r"(d[21]), "r"(d[22]), "r"(d[23]),
-                                   "r"(d[24]), "r"(d[25]), "r"(d[26]), "r"(d[27]), "r"(d[28]), "r"(d[29]), "r"(d[30]), "r"(d[31]) : "memory");
+                    for (int i = 0; i < 16; ++i) d[i] = finite ? d[i] : 0u;
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                                 ::"r"(dcol + h * 16), "r"(d[0]), "r"(d[1]), "r"(d[2]), "r"(d[3]), "r"(d[4]), "r"(d[5]), "r"(d[6]), "r"(d[7]),
+                                   "r"(d[8]), "r"(d[9]), "r"(d[10]), "r"(d[11]), "r"(d[12]), "r"(d[13]), "r"(d[14]), "r"(d[15]) : "memory");
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
@@ -259,26 +268,36 @@ __global__ void __launch_bounds__(kTcThreads, 1) compress_paged_tc_kernel(const 
             vc.inv64 = f2dup(inv * kCellScale);
             vc.n = f2dup(n);
             vc.tab = tab;
-            // ---- pass 2: quantize and store quarter by quarter ---------------------------------------------------
+            // ---- pass 2: quantize and store quarter by quarter; the quarter's upper 16 columns are loaded while the
+            // previous half is quantized, its lower 16 while the upper half is ------------------------------------
             f2 rr = f2dup(0.f);
-#pragma unroll
-            for (int qt = 0; qt < 4; ++qt) {
-                uint32_t d[32];
-                tc_ld32(dcol + qt * 32, d);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                f2 y[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    y[i] = f2pack(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1]));
-                Packed q;
-                q.norm = n_out;
-                q.rnorm = 0.f;                                   // the residual norm is complete after the last quarter
-                if (is_v) {
-                    quantize_quarter_fast<VB, false, true>(y, vc, rr, q);
-                    if (w.live) store_v_fast<VB>(w.page + KPART, w.t, qt, q);
-                } else {
-                    quantize_quarter_fast<KB, QJL, false>(y, vc, rr, q);
-                    if (w.live) store_k_fast<KB, QJL>(w.page, w.t, qt, q);
+            {
+                uint32_t dhi[16], dlo[16];
+                tc_ld16(dcol + 16, dhi);
+#pragma unroll 1
+                for (int qt = 0; qt < 4; ++qt) {
+                    float cvh[4], cvl[4];
+                    uint32_t sg_hi, sg_lo;
+                    tc_wait_ld();
+                    tc_ld16(dcol + qt * 32, dlo);
+                    if (is_v) quantize_half_fast<false>(dhi, vc, rr, cvh, sg_hi);
+                    else quantize_half_fast<QJL>(dhi, vc, rr, cvh, sg_hi);
+                    tc_wait_ld();
+                    if (qt < 3) tc_ld16(dcol + (qt + 1) * 32 + 16, dhi);
+                    if (is_v) quantize_half_fast<false>(dlo, vc, rr, cvl, sg_lo);
+                    else quantize_half_fast<QJL>(dlo, vc, rr, cvl, sg_lo);
+                    const float cv[8] = {cvl[0], cvl[1], cvl[2], cvl[3], cvh[0], cvh[1], cvh[2], cvh[3]};
+                    Packed q;
+                    q.norm = n_out;
+                    q.rnorm = 0.f;                               // the residual norm is complete after the last quarter
+                    q.signs = QJL ? ~prmt(sg_lo, sg_hi, 0x5410) : 0u;
+                    if (is_v) {
+                        assemble_indices<VB, true>(cv, q);
+                        if (w.live) store_v_fast<VB>(w.page + KPART, w.t, qt, q);
+                    } else {
+                        assemble_indices<KB, false>(cv, q);
+                        if (w.live) store_k_fast<KB, QJL>(w.page, w.t, qt, q);
+                    }
                 }
             }
             if constexpr (QJL) {
