@@ -154,7 +154,7 @@ def test_host_only_entry_points():
     assert cp == 256
     assert L.tq_decode_workspace_bytes(64, 64, 8, 512, cp) == 64 * 8 * ((512 + cp - 1) // cp) * 8 * 130 * 4
     assert L.tq_decode_auto_chunk_pages(1, 8, 32, 1) == 1
-    assert L.tq_decode_auto_chunk_pages(64, 1, 8, 512) == 64          # one KV head per GPU: 8 chunks of 64 pages
+    assert L.tq_decode_auto_chunk_pages(64, 1, 8, 512) == 57          # one KV head per GPU: 9 chunks fill the 592 CTA slots
     assert L.tq_decode_auto_chunk_pages(1, 8, 32, 256) == 16         # a single sequence: small chunks fill the GPU
     assert L.tq_decode_auto_chunk_pages(256, 8, 32, 4096) == 256     # skewed long sequences: capped
     assert L.tq_packed_attention_auto_splits(64, 32768) >= 1
