@@ -351,11 +351,12 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
         return head_base + static_cast<int64_t>(blk) * p.block_stride + sub * PAGE;
     };
     // Dense mode: one copy of the whole page.  Sparse mode: K part now, V part on demand.
-    auto issue_k = [&](int j) {
+    // whole = K and V parts in one copy (always in dense mode; in sparse mode when the V part is expected to be needed)
+    auto issue_k = [&](int j, bool whole = true) {
         const uint8_t* src = page_src(j);
         const int s = j % NSTAGE;
         if (lane == 0) {
-            constexpr uint32_t bytes = SPARSE ? KPART : PAGE;
+            const uint32_t bytes = (SPARSE && !whole) ? KPART : PAGE;
             mbar_expect_tx(mybar + s, bytes);
             bulk_g2s(myring + s * PAGE, src, bytes, mybar + s);
         }
@@ -422,6 +423,9 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     float al_lag0 = 1.f, al_lag1 = 1.f;
     bool lag_do_v = false;
     int lag_valid = kPageTokens;
+    uint32_t v_with_k = (1u << NSTAGE) - 1u;  // sparse mode, bit s: the page in stage s brought its V part along (the first pages do)
+    int pending_issue = -1;                   // sparse mode: page whose copy waits for a late V part to be used up
+    bool pending_whole = true;
 
     auto wait_v = [&](int j) -> bool {
         const int s = j % NSTAGE;
@@ -571,27 +575,44 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
                 issue_k(j + NSTAGE);
             }
         } else {
-            // The V copy of this page is issued now and consumed one iteration later, behind the K work of
-            // the next page.  Weights kept for the lagged page stay relative to the running maximum: they
-            // are rescaled together with the accumulator whenever the maximum grows.
-            if (do_v) issue_v(j);
-            if (j > 0) {
+            // A page whose V part came along with its K part (requested when the page NSTAGE before it needed its V)
+            // is used at once, exactly as in dense mode.  A page that turns out to need a V part it did not bring
+            // requests it now and is accumulated one iteration later, behind the next page's K work; the weights kept
+            // for it stay relative to the running maximum (rescaled with the accumulator when the maximum grows).
+            if (j > 0 && lag_do_v) {
                 if (__any_sync(0xffffffffu, grew)) {
                     lag_p[0] *= al_lag0; lag_p[1] *= al_lag1; lag_p[2] *= al_lag0; lag_p[3] *= al_lag1;
                 }
-                if (lag_do_v) {
-                    if (!wait_v(j - 1)) { timed_out = true; j_stop = j; break; }
-                    accumulate_v(j - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], kPageTokens);
-                }
+                if (!wait_v(j - 1)) { timed_out = true; j_stop = j; break; }
+                accumulate_v(j - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], kPageTokens);
                 __syncwarp();
-                if (j - 1 + NSTAGE < n_my) {
-                    if (j - 1 + NSTAGE >= jbase + 32) load_bt(jbase + 16);
-                    issue_k(j - 1 + NSTAGE);
+                lag_do_v = false;
+                if (pending_issue >= 0 && pending_issue < n_my) {
+                    if (pending_issue >= jbase + 32) load_bt(jbase + 16);
+                    issue_k(pending_issue, pending_whole);
+                    v_with_k = pending_whole ? (v_with_k | (1u << (pending_issue % NSTAGE))) : (v_with_k & ~(1u << (pending_issue % NSTAGE)));
                 }
+                pending_issue = -1;
             }
-            lag_p[0] = p0v; lag_p[1] = p1v; lag_p[2] = p2v; lag_p[3] = p3v;
-            lag_do_v = do_v;
-            lag_valid = valid_tokens;
+            const bool have_v = (v_with_k >> s) & 1u;
+            if (do_v && have_v) {
+                accumulate_v(j, p0v, p1v, p2v, p3v, valid_tokens);
+                __syncwarp();
+            } else if (do_v) {
+                issue_v(j);
+                lag_p[0] = p0v; lag_p[1] = p1v; lag_p[2] = p2v; lag_p[3] = p3v;
+                lag_do_v = true;
+                lag_valid = valid_tokens;
+            }
+            // next page for this stage: bring its V part along when this page needed its own
+            if (lag_do_v) {
+                pending_issue = j + NSTAGE;      // the stage is still in use until the late V part has been accumulated
+                pending_whole = true;
+            } else if (j + NSTAGE < n_my) {
+                if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
+                issue_k(j + NSTAGE, do_v);
+                v_with_k = do_v ? (v_with_k | (1u << s)) : (v_with_k & ~(1u << s));
+            }
         }
     }
     if constexpr (SPARSE) {
