@@ -129,8 +129,10 @@ def test_decode_peaked_logits_and_sparse_v():
     bt = torch.arange(125, dtype=torch.int32).reshape(1, 125).to(DEV)
     q = (torch.randn(1, 8, 128, generator=torch.Generator().manual_seed(1)) * 40).half().to(DEV)
     stats = torch.zeros(2, dtype=torch.int32, device=DEV)
+    # one chunk, so that every warp streams 32 pages: a warp's first four pages are always fetched whole, after
+    # that the V part of a page is only fetched while pages are being used
     paged_decode_attention(q, cache, bt, torch.tensor([2000], dtype=torch.int32, device=DEV), books, 16,
-                           sparse_thresh=1e-6, skip_stats=stats)
+                           sparse_thresh=1e-6, skip_stats=stats, chunk_pages=128)
     seen, skipped = stats.cpu().tolist()
     assert seen == 125 and 0 < skipped < seen
 
@@ -176,7 +178,7 @@ def test_decode_length_beyond_block_table_is_cut_and_flagged(chunk):
     assert_attn_close(out2.float().cpu().numpy(), ref)
 
 
-def _slice_case(fmt, lens, G, thresh, qscale, seed, bias_pages=0.0):
+def _slice_case(fmt, lens, G, thresh, qscale, seed, bias_pages=0.0, chunk_pages=256):
     """One KV head, `G` query heads, sequences of the given lengths over a shared random page pool."""
     books = Codebooks(fmt, DEV)
     lens_t = torch.tensor(lens, dtype=torch.int32)
@@ -198,8 +200,10 @@ def _slice_case(fmt, lens, G, thresh, qscale, seed, bias_pages=0.0):
     q = (torch.randn(len(lens), G, 128, generator=g) * qscale).half()
     sm, cs = 1 / math.sqrt(128), math.sqrt(math.pi / 2) / 128
     stats = torch.zeros(2, dtype=torch.int32, device=DEV) if thresh > 0 else None
+    # chunks of 256 pages, as the launcher picks for the full batch of this workload (the two-sequence slice alone
+    # would get 16-page chunks, where every page is among a warp's first four and is fetched whole)
     out = paged_decode_attention(q.to(DEV), cache, bt.to(DEV), lens_t.to(DEV), books, 16, sm, cs, sparse_thresh=thresh,
-                                 skip_stats=stats)
+                                 skip_stats=stats, chunk_pages=chunk_pages)
     torch.cuda.synchronize()
     assert _native.read_status(DEV) == 0
     ref = oracle_decode(q, None, f, fmt, books, bt, lens_t, sm, cs, 16)        # dense fp32 truth

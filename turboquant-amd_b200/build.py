@@ -34,7 +34,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build(verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(os.path.dirname(LIB), exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".inc"))]
     headers.append(os.path.join(HERE, "..", "include", "tq_b200.h"))
     headers.append(os.path.abspath(__file__))
 

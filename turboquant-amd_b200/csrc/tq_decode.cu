@@ -416,16 +416,10 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 #pragma unroll
         for (int r = 0; r < 4; ++r) oacc[i][r] = 0.f;
     bool timed_out = false;
-    uint32_t v_seen = 0, v_skipped = 0;
+    uint32_t v_skipped = 0;
     uint32_t v_parity = 0;                  // bit s: phase of the V barrier of stage s (sparse mode)
     int j_stop = n_my;
-    float lag_p[4] = {0.f, 0.f, 0.f, 0.f};   // sparse mode: weights of the page whose V part is still in flight
-    float al_lag0 = 1.f, al_lag1 = 1.f;
-    bool lag_do_v = false;
-    int lag_valid = kPageTokens;
     uint32_t v_with_k = (1u << NSTAGE) - 1u;  // sparse mode, bit s: the page in stage s brought its V part along (the first pages do)
-    int pending_issue = -1;                   // sparse mode: page whose copy waits for a late V part to be used up
-    bool pending_whole = true;
 
     auto wait_v = [&](int j) -> bool {
         const int s = j % NSTAGE;
@@ -463,162 +457,20 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     };
 
     for (int j = 0; j < n_my; ++j) {
-        const int s = j % NSTAGE;
-        const uint32_t parity = (j / NSTAGE) & 1;
-        const uint32_t stage = s * PAGE;
-        if (!mbar_wait_bounded(mybar + s, parity)) {
-            timed_out = true;
-            j_stop = j;
-            break;
-        }
-        const int valid_tokens = min(kPageTokens, L - (p0 + warp + kWarps * j) * kPageTokens);
-
-        // ---- K: dequantise two token rows (gid, gid + 8) and score them against 8 queries
-        uint32_t wa[NWK], wb[NWK];
-        lds_words<NWK, 0>(ring_k + stage, wa);
-        lds_words<NWK, 32 * NWK * 4>(ring_k + stage, wb);
-        uint32_t mwa[4], mwb[4];
-        {
-            uint32_t ia[KB], ib[KB];
-#pragma unroll
-            for (int i = 0; i < KB; ++i) { ia[i] = wa[i]; ib[i] = wb[i]; }
-            masked_words<KB>(ia, mwa);
-            masked_words<KB>(ib, mwb);
-        }
-        float sm[4] = {0.f, 0.f, 0.f, 0.f};
-        float sq[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const uint32_t a0 = lut_pair(klut, mwa[c >> 1], 2 * (c & 1)), a1 = lut_pair(klut, mwa[c >> 1], 2 * (c & 1) + 1);
-            const uint32_t b0 = lut_pair(klut, mwb[c >> 1], 2 * (c & 1)), b1 = lut_pair(klut, mwb[c >> 1], 2 * (c & 1) + 1);
-            mma_f16_16816(sm, a0, b0, a1, b1, qf[2 * c], qf[2 * c + 1]);
-        }
-        float sq2[4] = {0.f, 0.f, 0.f, 0.f};
-        if constexpr (QJL) {
-            sq[0] = sq[2] = sq_init0;
-            sq[1] = sq[3] = sq_init1;
-#pragma unroll
-            for (int ki = 0; ki < 4; ++ki) {
-                const uint32_t xa = wa[KB] << (4 * ki), xb = wb[KB] << (4 * ki);
-                mma_f16_16816(sq, (xa & 0x80008000u) | 0x3C003C00u, (xb & 0x80008000u) | 0x3C003C00u,
-                              xa & 0x40004000u, xb & 0x40004000u, qpf[4 * ki], qpf[4 * ki + 1]);
-                mma_f16_16816(sq2, xa & 0x20002000u, xb & 0x20002000u, xa & 0x10001000u, xb & 0x10001000u,
-                              qpf[4 * ki + 2], qpf[4 * ki + 3]);
-            }
-        }
-        // The softmax scale (and log2 e) is applied to the fp32 norms, not to the fp16 query, so the
-        // query fragments are the caller's fp16 values exactly.
-        float2 kn = unpack_half2(lds_u32<KN_OFF>(ring_n + stage));
-        kn.x *= p.qscale;
-        kn.y *= p.qscale;
-        float s0 = sm[0] * kn.x, s1 = sm[1] * kn.x, s2 = sm[2] * kn.y, s3 = sm[3] * kn.y;
-        if constexpr (QJL) {
-            float2 krn = unpack_half2(lds_u32<KRN_OFF>(ring_n + stage));
-            krn.x *= p.qpscale;
-            krn.y *= p.qpscale;
-            s0 = fmaf(sq[0] + sq2[0], krn.x, s0);
-            s1 = fmaf(sq[1] + sq2[1], krn.x, s1);
-            s2 = fmaf(sq[2] + sq2[2], krn.y, s2);
-            s3 = fmaf(sq[3] + sq2[3], krn.y, s3);
-        }
-        // only the last page of a sequence can be partly filled
-        if (valid_tokens < kPageTokens) {
-            if (gid >= valid_tokens) { s0 = -INFINITY; s1 = -INFINITY; }
-            if (gid + 8 >= valid_tokens) { s2 = -INFINITY; s3 = -INFINITY; }
-        }
-
-        // ---- online softmax over the 16 tokens (rows live across the 8 gid lanes)
-        float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-        }
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const bool grew = (mn0 > m0) || (mn1 > m1);
-        float p0v = ex2(s0 - mn0), p1v = ex2(s1 - mn1), p2v = ex2(s2 - mn0), p3v = ex2(s3 - mn1);
-        if (__any_sync(0xffffffffu, grew)) {
-            const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
-            al_lag0 = al0;
-            al_lag1 = al1;
-            l0 *= al0;
-            l1 *= al1;
-            // accumulator rows belong to query gid: fetch its factor from the lane that scored it
-            const float t0 = __shfl_sync(0xffffffffu, al0, gid >> 1);
-            const float t1 = __shfl_sync(0xffffffffu, al1, gid >> 1);
-            const float ag = (gid & 1) ? t1 : t0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) oacc[i][r] *= ag;
-            m0 = mn0;
-            m1 = mn1;
-        }
-        l0 += p0v + p2v;
-        l1 += p1v + p3v;
-
-        // ---- Sparse-V: skip the page when no weight of the group exceeds the threshold
-        bool do_v = true;
         if constexpr (SPARSE) {
-            // p = 2^(s - m) in the log2 domain; compare exponents to avoid a second exp.
-            const float e = fmaxf(fmaxf(s0 - mn0, s1 - mn1), fmaxf(s2 - mn0, s3 - mn1));
-            do_v = __any_sync(0xffffffffu, e > p.log2_thresh);
-            ++v_seen;
-            if (!do_v) ++v_skipped;
-        }
-        if constexpr (!SPARSE) {
-            accumulate_v(j, p0v, p1v, p2v, p3v, valid_tokens);
-            __syncwarp();
-            if (j + NSTAGE < n_my) {
-                // slide the window by 16 so that entries j .. j + NSTAGE stay available
-                if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
-                issue_k(j + NSTAGE);
+            if ((v_with_k >> (j % NSTAGE)) & 1u) {
+#define TQ_PAGE_HAVE_V 1
+#include "tq_decode_page.inc"
+#undef TQ_PAGE_HAVE_V
+            } else {
+#define TQ_PAGE_HAVE_V 0
+#include "tq_decode_page.inc"
+#undef TQ_PAGE_HAVE_V
             }
         } else {
-            // A page whose V part came along with its K part (requested when the page NSTAGE before it needed its V)
-            // is used at once, exactly as in dense mode.  A page that turns out to need a V part it did not bring
-            // requests it now and is accumulated one iteration later, behind the next page's K work; the weights kept
-            // for it stay relative to the running maximum (rescaled with the accumulator when the maximum grows).
-            if (j > 0 && lag_do_v) {
-                if (__any_sync(0xffffffffu, grew)) {
-                    lag_p[0] *= al_lag0; lag_p[1] *= al_lag1; lag_p[2] *= al_lag0; lag_p[3] *= al_lag1;
-                }
-                if (!wait_v(j - 1)) { timed_out = true; j_stop = j; break; }
-                accumulate_v(j - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], kPageTokens);
-                __syncwarp();
-                lag_do_v = false;
-                if (pending_issue >= 0 && pending_issue < n_my) {
-                    if (pending_issue >= jbase + 32) load_bt(jbase + 16);
-                    issue_k(pending_issue, pending_whole);
-                    v_with_k = pending_whole ? (v_with_k | (1u << (pending_issue % NSTAGE))) : (v_with_k & ~(1u << (pending_issue % NSTAGE)));
-                }
-                pending_issue = -1;
-            }
-            const bool have_v = (v_with_k >> s) & 1u;
-            if (do_v && have_v) {
-                accumulate_v(j, p0v, p1v, p2v, p3v, valid_tokens);
-                __syncwarp();
-            } else if (do_v) {
-                issue_v(j);
-                lag_p[0] = p0v; lag_p[1] = p1v; lag_p[2] = p2v; lag_p[3] = p3v;
-                lag_do_v = true;
-                lag_valid = valid_tokens;
-            }
-            // next page for this stage: bring its V part along when this page needed its own
-            if (lag_do_v) {
-                pending_issue = j + NSTAGE;      // the stage is still in use until the late V part has been accumulated
-                pending_whole = true;
-            } else if (j + NSTAGE < n_my) {
-                if (j + NSTAGE >= jbase + 32) load_bt(jbase + 16);
-                issue_k(j + NSTAGE, do_v);
-                v_with_k = do_v ? (v_with_k | (1u << s)) : (v_with_k & ~(1u << s));
-            }
-        }
-    }
-    if constexpr (SPARSE) {
-        if (!timed_out && n_my > 0 && lag_do_v) {
-            if (wait_v(n_my - 1)) accumulate_v(n_my - 1, lag_p[0], lag_p[1], lag_p[2], lag_p[3], lag_valid);
-            else timed_out = true;
+#define TQ_PAGE_HAVE_V 1
+#include "tq_decode_page.inc"
+#undef TQ_PAGE_HAVE_V
         }
     }
     if (timed_out) {
@@ -635,7 +487,7 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     }
     if constexpr (SPARSE) {
         if (p.skip_stats && lane == 0) {
-            atomicAdd(p.skip_stats, v_seen);
+            atomicAdd(p.skip_stats, static_cast<uint32_t>(j_stop));   // pages this warp visited
             atomicAdd(p.skip_stats + 1, v_skipped);
         }
     }
