@@ -83,10 +83,10 @@ def test_polarquant_dict_contract():
         polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=3), torch.eye(128, device=DEV))
 
 
+@pytest.mark.parametrize("n", [4099, 16805])   # generic kernel / persistent table-driven kernel (more than 16384 rows); both ragged
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-def test_compress_k_v_contiguous_vs_oracle(bits, dtype):
-    n = 4099                                   # ragged: not a multiple of the 4 vectors a CTA takes
+def test_compress_k_v_contiguous_vs_oracle(bits, dtype, n):
     x = _inputs(n, seed=bits).to(dtype)
     c, b = make_codebook(128, bits)
     H = make_wht_matrix(128)
@@ -118,6 +118,33 @@ def test_compress_k_v_contiguous_vs_oracle(bits, dtype):
         gotv = packed_compress.unpack_indices(v_idx.cpu(), bits).numpy()
         assert (gotv != O.unpack_indices(ov_idx, bits)).mean() <= 1e-4
         assert torch.equal(v_idx, k_idx) and torch.equal(v_n, k_n)   # V is the K computation without the residual
+
+
+@pytest.mark.parametrize("rotate", [False, True])
+def test_compress_contiguous_large_tight_codebook_and_nonfinite_rows(rotate):
+    """More than 16384 rows take the persistent kernel.  A codebook with two boundaries closer than 1/64 makes it fall
+    back to the binary search inside the kernel; a NaN / Inf row spoils only itself."""
+    n = 16805
+    x = _inputs(n, seed=5).half()
+    x[17, 5] = float("nan")
+    x[n - 1, 100] = float("inf")
+    rot = O.make_wht_matrix(128) if rotate else None
+    PiT = make_wht_matrix(128).to(DEV) if rotate else None
+    for tight in (False, True):
+        c, b = make_codebook(128, 3)
+        if tight:
+            b = b.clone()
+            b[3] = b[2] + 1e-3
+        k_idx, k_sg, k_rn, k_n = packed_compress.compress_k(x.to(DEV), PiT, None, c.to(DEV), b.to(DEV))
+        good = np.ones(n, dtype=bool)
+        good[[17, n - 1]] = False
+        o_idx, o_sg, o_rn, o_n = O.compress_k_packed(x.float().numpy()[good], c.numpy(), b.numpy(), 3, rot, permuted=False)
+        got = packed_compress.unpack_indices(k_idx.cpu(), 3).numpy()[good]
+        want = O.unpack_indices(o_idx, 3)
+        assert (got != want).mean() <= (1e-4 if rotate else 1e-6) and np.abs(got.astype(int) - want).max() <= 1
+        assert (np.unpackbits(k_sg.cpu().numpy()[good], axis=1) != np.unpackbits(o_sg, axis=1)).mean() <= (1e-4 if rotate else 1e-5)
+        assert _half_ulp_close(k_n.cpu()[torch.from_numpy(good)], o_n.astype(np.float32))
+        assert not torch.isfinite(k_n[17].float()) and not torch.isfinite(k_n[n - 1].float())
 
 
 def test_compress_empty_and_single():

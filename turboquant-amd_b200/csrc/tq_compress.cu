@@ -384,14 +384,36 @@ __device__ __forceinline__ void store_idx_contig(uint8_t* row, int quarter, cons
     }
 }
 
+// Sign bits and norms of one packed row (this lane's quarter).  signs: bit l = 1 when the residual of local dim l is >= 0.
+template <bool QJL>
+__device__ __forceinline__ void store_contig_tail(const ContigParams& p, int64_t row, int quarter, uint32_t signs, float norm,
+                                                  float rnorm) {
+    if constexpr (QJL) {
+        uint8_t* srow = p.sign_out + row * 16;
+        if (p.permute) {
+            // stride-4 order: output bit 32 c + i <- dim c + 4 i.  This lane's dim 32 q + l has
+            // c = l & 3 and i = 8 q + (l >> 2): it fills byte q of each of the four 32-bit words.
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v = 0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v |= ((signs >> (4 * k + c)) & 1u) << k;
+                srow[4 * c + quarter] = static_cast<uint8_t>(v);
+            }
+        } else {
+            reinterpret_cast<uint32_t*>(srow)[quarter] = signs;   // byte j bit b <- dim 8 j + b
+        }
+        if (quarter == 0) p.rnorm_h[row] = __float2half_rn(rnorm);
+    }
+    if (quarter == 0) p.norm_h[row] = __float2half_rn(norm);
+}
+
+// One group of 8 rows per warp on the generic quantizer (binary-search bucketize over arbitrary sorted boundaries).
+// Lanes of rows past the end still take part in the shuffles (on zeros) and store nothing.
 template <int BITS, OutMode MODE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) compress_contig_kernel(const ContigParams p) {
+__device__ __forceinline__ void compress_contig_rows(const ContigParams& p, int64_t row, int lane, const float* csm) {
     constexpr bool QJL = MODE != OutMode::kPackedV;
-    __shared__ float csm[1 << BITS];
-    if (threadIdx.x < (1 << BITS)) csm[threadIdx.x] = p.c ? p.c[threadIdx.x] : 0.f;
-    __syncthreads();
-    const int lane = threadIdx.x & 31, quarter = lane & 3;
-    const int64_t row = (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2);
+    const int quarter = lane & 3;
     const bool live = row < p.n;
     Boundaries<BITS> bd;
     bd.load(p.b);
@@ -436,25 +458,111 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) compress_contig_kernel(cons
         quantize_quarter<BITS, QJL>(x, p.rotate != 0, lane, bd, csm, q);
         if (!live) return;
         store_idx_contig<BITS>(p.idx_out + row * (16 * BITS), quarter, q.idx);
-        if constexpr (QJL) {
-            uint8_t* srow = p.sign_out + row * 16;
-            if (p.permute) {
-                // stride-4 order: output bit 32 c + i <- dim c + 4 i.  This lane's dim 32 q + l has
-                // c = l & 3 and i = 8 q + (l >> 2): it fills byte q of each of the four 32-bit words.
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v = 0;
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) v |= ((q.signs >> (4 * k + c)) & 1u) << k;
-                    srow[4 * c + quarter] = static_cast<uint8_t>(v);
-                }
-            } else {
-                reinterpret_cast<uint32_t*>(srow)[quarter] = q.signs;   // byte j bit b <- dim 8 j + b
-            }
-            if (quarter == 0) p.rnorm_h[row] = __float2half_rn(q.rnorm);
-        }
-        if (quarter == 0) p.norm_h[row] = __float2half_rn(q.norm);
+        store_contig_tail<QJL>(p, row, quarter, q.signs, q.norm, q.rnorm);
     }
+}
+
+template <int BITS, OutMode MODE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) compress_contig_kernel(const ContigParams p) {
+    __shared__ float csm[1 << BITS];
+    if (threadIdx.x < (1 << BITS)) csm[threadIdx.x] = p.c ? p.c[threadIdx.x] : 0.f;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    compress_contig_rows<BITS, MODE>(
+        p, (static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5)) * kItemsPerWarp + (lane >> 2), lane, csm);
+}
+
+// ---- packed contiguous outputs on the table-driven quantizer ------------------------------------------------------
+// Persistent CTAs of 16 warps, one per SM, as the paged kernel: the table is built once per CTA, which then strides over
+// groups of 128 rows, 8 per warp.  fp16 / bf16 rows that still need the rotation are staged through two buffers per
+// warp, two groups ahead, and rotated on the tensor cores; fp32 and already rotated rows take plain loads.
+template <int BITS, bool QJL>
+__device__ __forceinline__ void store_contig_fast(const ContigParams& p, int64_t row, int quarter, const Packed& q) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(p.idx_out + row * (16 * BITS) + quarter * (4 * BITS));
+    if constexpr (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(q.word[0], q.word[1], q.word[2], q.word[3]);
+    else if constexpr (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(q.word[0], q.word[1]);
+    else {
+#pragma unroll
+        for (int j = 0; j < BITS; ++j) dst[j] = q.word[j];
+    }
+    store_contig_tail<QJL>(p, row, quarter, q.signs, q.norm, q.rnorm);
+}
+
+template <int BITS, bool QJL>
+__global__ void __launch_bounds__(kFastWarps * 32, 1) compress_contig_fast_kernel(const ContigParams p, int64_t n_groups) {
+    extern __shared__ __align__(128) unsigned char tables[];
+    __shared__ float csm[1 << BITS];
+    __shared__ int bad;
+    if (threadIdx.x == 0) bad = 0;
+    if (threadIdx.x < (1 << BITS)) csm[threadIdx.x] = p.c ? p.c[threadIdx.x] : 0.f;
+    __syncthreads();
+    build_table<BITS, QJL>(tables, p.b, p.c, &bad);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, quarter = lane & 3, warp = threadIdx.x >> 5;
+    const int64_t row0 = warp * kItemsPerWarp + (lane >> 2);   // + group * 128
+    if (bad != 0) {   // two boundaries inside one cell: the generic quantizer
+        const ContigParams pc = p;
+        for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x)
+            compress_contig_rows<BITS, QJL ? OutMode::kPackedK : OutMode::kPackedV>(pc, grp * kFastItemsPerCta + row0, lane, csm);
+        return;
+    }
+    constexpr uint32_t kBias = kMagicBits * static_cast<uint32_t>(kCellStride);   // modulo 2^32
+    const uint32_t tab = smem_u32(tables) + (QJL ? (lane & 7) * 16 : (lane & 15) * 8) - kBias;
+    Packed q;
+    if (p.rotate && p.in_dtype != TQ_DTYPE_F32) {
+        const bool bf16 = p.in_dtype == TQ_DTYPE_BF16;
+        uint4* buf = reinterpret_cast<uint4*>(tables + kTableBytes + warp * kStagePerWarp);   // two buffers of 128 uint4
+        const WhtFragments hf = make_wht_fragments(lane, bf16);
+        int64_t grp = blockIdx.x;
+        const int64_t step = gridDim.x;
+        {
+            const int64_t r0 = grp * kFastItemsPerCta + row0, r1 = (grp + step) * kFastItemsPerCta + row0;
+            stage_row(buf, lane, p.x, r0 * kHeadDim + 32 * quarter, r0 < p.n);
+            stage_row(buf + 128, lane, p.x, r1 * kHeadDim + 32 * quarter, grp + step < n_groups && r1 < p.n);
+        }
+        int cur = 0;
+        for (; grp < n_groups; grp += step, cur ^= 1) {
+            const int64_t row = grp * kFastItemsPerCta + row0;
+            const int64_t nxt = (grp + 2 * step) * kFastItemsPerCta + row0;
+            const bool nxt_live = grp + 2 * step < n_groups && nxt < p.n;
+            uint4* b = buf + 128 * cur;
+            wait_staged();
+            compress_row_mma<BITS, QJL, false, true>(smem_u32(b + lane), row < p.n, lane, bf16, hf, tab, q, [&] {
+                stage_row(b, lane, p.x, nxt * kHeadDim + 32 * quarter, nxt_live);
+            });
+            if (row < p.n) store_contig_fast<BITS, QJL>(p, row, quarter, q);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        const bool rotate = p.rotate != 0;
+        const float scale = rotate ? kWhtScale : 1.f, inv_scale = rotate ? 11.313708498984761f : 1.f;
+        for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+            const int64_t row = grp * kFastItemsPerCta + row0;
+            f2 y[16];
+            fetch_plain(p.x, row * kHeadDim + 32 * quarter, row < p.n, p.in_dtype, rotate, lane, y);
+            quantize_fast<BITS, QJL, false, true>(y, scale, inv_scale, tab, q);
+            if (row < p.n) store_contig_fast<BITS, QJL>(p, row, quarter, q);
+        }
+    }
+}
+
+template <int BITS, bool QJL>
+int launch_contig_fast(const ContigParams& p, cudaStream_t st) {
+    const int64_t n_groups = (p.n + kFastItemsPerCta - 1) / kFastItemsPerCta;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TQ_ERR_LAUNCH;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TQ_ERR_LAUNCH;
+    const unsigned grid = static_cast<unsigned>(n_groups < sms ? n_groups : sms);
+    constexpr int kSmem = kTableBytes + kFastWarps * kStagePerWarp;
+    static bool configured[64] = {false};
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        if (cudaFuncSetAttribute(compress_contig_fast_kernel<BITS, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+            cudaSuccess)
+            return TQ_ERR_LAUNCH;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    compress_contig_fast_kernel<BITS, QJL><<<grid, kFastWarps * 32, kSmem, st>>>(p, n_groups);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
 template <int KB, int VB>
@@ -474,6 +582,18 @@ int launch_paged_v(const PagedParams& p, int vb, bool qjl, cudaStream_t st) {
 
 template <OutMode MODE>
 int launch_contig(const ContigParams& p, int bits, cudaStream_t st) {
+    if constexpr (MODE != OutMode::kUnpacked) {
+        // large packed launches: the persistent table-driven kernel (small ones would mostly build its table)
+        if (p.n > kSmallLaunchItems) {
+            constexpr bool QJL = MODE == OutMode::kPackedK;
+            switch (bits) {
+                case 2: return launch_contig_fast<2, QJL>(p, st);
+                case 3: return launch_contig_fast<3, QJL>(p, st);
+                case 4: return launch_contig_fast<4, QJL>(p, st);
+                default: return TQ_ERR_UNSUPPORTED;
+            }
+        }
+    }
     const unsigned grid = static_cast<unsigned>((p.n + kItemsPerCta - 1) / kItemsPerCta);
     switch (bits) {
         case 2: compress_contig_kernel<2, MODE><<<grid, kWarpsPerCta * 32, 0, st>>>(p); break;

@@ -272,12 +272,38 @@ __device__ __forceinline__ void assemble_indices(const float (&cv)[8], Packed& o
     }
 }
 
+// Contiguous outputs (reference byte layouts: 2-bit four per byte LSB first, 4-bit low nibble first, 3-bit a
+// little-endian bit stream): cv[c] holds the four indices of chunk c densely, idx_e at bit BITS * e, so a chunk is
+// 4 * BITS bits of the lane's BITS output words.
+template <int BITS>
+__device__ __forceinline__ void assemble_contig(const float (&cv)[8], Packed& out) {
+    const float kInt = 8388608.f;
+    uint32_t u[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) u[c] = __float_as_uint(cv[c] + kInt);   // 0x4B000000 | value
+    if constexpr (BITS == 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out.word[j] = prmt(u[2 * j], u[2 * j + 1], 0x5410);
+    } else if constexpr (BITS == 2) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            out.word[j] = prmt(prmt(u[4 * j], u[4 * j + 1], 0x0040), prmt(u[4 * j + 2], u[4 * j + 3], 0x0040), 0x5410);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) u[c] &= 0xfffu;
+        out.word[0] = u[0] | (u[1] << 12) | (u[2] << 24);
+        out.word[1] = (u[2] >> 8) | (u[3] << 4) | (u[4] << 16) | (u[5] << 28);
+        out.word[2] = (u[5] >> 4) | (u[6] << 8) | (u[7] << 20);
+    }
+}
+
 // y: this lane's 32 rotated values as 16 pairs of adjacent dims, still to be multiplied by `scale` (2^-3.5 after
 // the unnormalised WHT, else 1).  tab: shared address of this lane's copy of cell 0, minus kMagicBits * 128.
 // The scale is applied to the norm only: u = (scale y) / (n + 1e-8) is computed as y / ((n + 1e-8) / scale),
 // which is the same number up to the rounding the rotation itself carries; with scale = 1 nothing changes.
-template <int BITS, bool QJL, bool ISV>
+template <int BITS, bool QJL, bool ISV, bool CONTIG = false>
 __device__ __forceinline__ void quantize_fast(f2 (&y)[16], float scale, float inv_scale, uint32_t tab, Packed& out) {
+    constexpr float kStep = CONTIG ? static_cast<float>(1 << BITS) : 16.f;   // spacing of a chunk's four indices
     f2 sa = f2dup(0.f), sb = f2dup(0.f);
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
@@ -314,9 +340,10 @@ __device__ __forceinline__ void quantize_fast(f2 (&y)[16], float scale, float in
         float k0, k1, k2, k3;
         quant_pair<QJL>(y[2 * c + 1], vc, rr, sg[c >> 2], k2, k3);
         quant_pair<QJL>(y[2 * c], vc, rr, sg[c >> 2], k0, k1);
-        cv[c] = fmaf(fmaf(fmaf(k3, 16.f, k2), 16.f, k1), 16.f, k0);
+        cv[c] = fmaf(fmaf(fmaf(k3, kStep, k2), kStep, k1), kStep, k0);
     }
-    assemble_indices<BITS, ISV>(cv, out);
+    if constexpr (CONTIG) assemble_contig<BITS>(cv, out);
+    else assemble_indices<BITS, ISV>(cv, out);
     if constexpr (QJL) {
         float ra, rb;
         out.signs = ~prmt(sg[0], sg[1], 0x5410);
@@ -403,9 +430,10 @@ __device__ __forceinline__ void read_staged(uint32_t row, bool live, uint32_t (&
 
 // after_read() is called once the staged row has been read for the last time (the caller requests the next row
 // into the same buffer there).
-template <int BITS, bool QJL, bool ISV, class AfterRead>
+template <int BITS, bool QJL, bool ISV, bool CONTIG = false, class AfterRead>
 __device__ __forceinline__ void compress_row_mma(uint32_t row, bool live, int lane, bool bf16, const WhtFragments& hf,
                                                  uint32_t tab, Packed& out, AfterRead after_read) {
+    constexpr float kStep = CONTIG ? static_cast<float>(1 << BITS) : 16.f;   // spacing of a chunk's four indices
     uint32_t w[16];
     read_staged(row, live, w);
     // ||x||^2: even words on the diagonal of rows 0..7 of da, odd words on that of rows 8..15 of db
@@ -467,11 +495,12 @@ __device__ __forceinline__ void compress_row_mma(uint32_t row, bool live, int la
             uint32_t nib = 0u;
             quant_pair<QJL, false>(y[2 * j + 1], vc, rr, nib, k2, k3);
             quant_pair<QJL, false>(y[2 * j], vc, rr, nib, k0, k1);
-            cv[c] = fmaf(fmaf(fmaf(k3, 16.f, k2), 16.f, k1), 16.f, k0);
+            cv[c] = fmaf(fmaf(fmaf(k3, kStep, k2), kStep, k1), kStep, k0);
             if constexpr (QJL) sg |= nib << (4 * c);
         }
     }
-    assemble_indices<BITS, ISV>(cv, out);
+    if constexpr (CONTIG) assemble_contig<BITS>(cv, out);
+    else assemble_indices<BITS, ISV>(cv, out);
     if constexpr (QJL) {
         float ra, rb;
         out.signs = ~sg;
