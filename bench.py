@@ -473,6 +473,82 @@ def time_bulk_compress(fmt_name: str, tokens: int, hkv: int, device, reps: int =
     return nbytes / (min(ms) / 1e3) / 1e9, min(ms) * 1e3
 
 
+def _graph_time_us(fn, reps: int = 10) -> float:
+    """Device time of fn() in microseconds: `reps` calls captured in one CUDA graph, CUDA events around the replay
+    (so that no Python or launch overhead sits between the kernels), best of three replays after a warm-up."""
+    fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fn()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                fn()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        e1.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3 / reps)
+    return best
+
+
+def time_packed_attention(device, bits: int = 3, BH: int = 64, Sk: int = 32768):
+    """The contiguous packed_attention call (one query per K/V stream, reference byte layouts) on random packed
+    fields: us per call (partial + merge kernels) and GB/s of packed bytes read."""
+    from turboquant.core import make_codebook
+    from turboquant.kernels import packed_attention as PA
+    g = torch.Generator(device=device).manual_seed(1)
+    c, _ = make_codebook(128, bits)
+    c = c.to(device)
+    k_idx = torch.randint(0, 256, (BH, Sk, 16 * bits), dtype=torch.uint8, device=device, generator=g)
+    k_sg = torch.randint(0, 256, (BH, Sk, 16), dtype=torch.uint8, device=device, generator=g)
+    v_idx = torch.randint(0, 256, (BH, Sk, 16 * bits), dtype=torch.uint8, device=device, generator=g)
+    k_rn = (torch.rand(BH, Sk, device=device, generator=g) * 3).half()
+    k_n = (torch.rand(BH, Sk, device=device, generator=g) * 4 + 8).half()
+    v_n = (torch.rand(BH, Sk, device=device, generator=g) * 4 + 8).half()
+    Q = (torch.randn(BH, 128, device=device, generator=g) / math.sqrt(128)).half()
+    Qp = (torch.randn(BH, 128, device=device, generator=g) / math.sqrt(128)).half()
+    cs = math.sqrt(math.pi / 2) / math.sqrt(128)
+    us = _graph_time_us(lambda: PA.packed_attention(Q, Qp, k_idx, k_sg, k_rn, k_n, v_idx, v_n, c, cs))
+    nbytes = BH * Sk * (32 * bits + 16 + 6)
+    return us, nbytes / us / 1e3
+
+
+def time_contiguous_compress(device, bits: int = 3, n: int = 1 << 20):
+    """compress_k / compress_v of n fp16 rows into the reference's contiguous packed arrays, rotation included:
+    (us, GB/s) each, bytes = rows read + packed fields written."""
+    from turboquant.core import make_codebook, make_wht_matrix
+    from turboquant.kernels import packed_compress
+    g = torch.Generator(device=device).manual_seed(2)
+    x = torch.randn(n, 128, device=device, generator=g).half()
+    x[:, OUTLIER_CHANNELS] *= 10
+    c, b = make_codebook(128, bits)
+    c, b, H = c.to(device), b.to(device), make_wht_matrix(128).to(device)
+    us_k = _graph_time_us(lambda: packed_compress.compress_k_permuted(x, H, None, c, b), reps=4)
+    us_v = _graph_time_us(lambda: packed_compress.compress_v(x, H, c, b), reps=4)
+    bk, bv = n * (256 + 16 * bits + 16 + 4), n * (256 + 16 * bits + 2)
+    return (us_k, bk / us_k / 1e3), (us_v, bv / us_v / 1e3)
+
+
+def measure_contiguous_api(device, peak: float) -> dict:
+    """Rows for the contiguous (non-paged) API of the reference's packed kernels."""
+    res = {}
+    us, gbs = time_packed_attention(device)
+    res["packed_attention"] = {"workload": "contiguous packed_attention, 3-bit + QJL, BH 64 x 32768 tokens (247 MB packed)",
+                               "us": us, "GBps": gbs, "frac_of_peak": gbs / peak}
+    (us_k, gk), (us_v, gv) = time_contiguous_compress(device)
+    res["compress_k_contiguous"] = {"workload": "compress_k, 3-bit + QJL, 1 048 576 fp16 rows, rotation in the kernel",
+                                    "us": us_k, "GBps": gk, "frac_of_peak": gk / peak}
+    res["compress_v_contiguous"] = {"workload": "compress_v, 3-bit, 1 048 576 fp16 rows, rotation in the kernel",
+                                    "us": us_v, "GBps": gv, "frac_of_peak": gv / peak}
+    return res
+
+
 def measure_other_workloads(device, peak: float, steps: int, warmup: int) -> dict:
     """The other single-GPU workloads, two layers each, measured in the same run (device-resident inputs, CUDA
     events, one CUDA graph per step): us/layer, GB/s of packed bytes, fraction of the measured peak."""
@@ -496,6 +572,7 @@ def measure_other_workloads(device, peak: float, steps: int, warmup: int) -> dic
     gbs, us = time_bulk_compress("turbo2", 1 << 20, 8, device)
     res["cfg5_compress_1M_tokens"] = {"workload": "turbo2 compress-and-scatter of 1 048 576 new tokens x 8 KV heads (fp16 K/V)",
                                       "us": us, "GBps": gbs, "frac_of_peak": gbs / peak, "pct_of_8TBps": 100 * gbs / 8000.0}
+    res.update(measure_contiguous_api(device, peak))
     return res
 
 
@@ -634,6 +711,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the other workloads' rows (single GPU only)")
+    ap.add_argument("--micro", action="store_true",
+                    help="only the contiguous-API rows (packed_attention, compress_k, compress_v): one JSON line, for small profiling runs")
     ap.add_argument("--decode-kernel", default="default", choices=["default", "tcgen05"],
                     help="tcgen05: time the opt-in tensor-memory variant in the device-resident leg (value / roofline)")
     args = ap.parse_args()
@@ -655,6 +734,10 @@ def main():
             raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if args.micro:
+        peak, peak_src = load_peak()
+        print(json.dumps({"micro": measure_contiguous_api(dev, peak), "peak_GBps": peak, "peak_source": peak_src}))
+        return
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
