@@ -17,12 +17,15 @@
 //    maximum is only raised when a score exceeds it by 2^8); slots, warps and splits are merged at the end.
 #include "tq_common.cuh"
 
+#include <cstdlib>
+
 namespace tq {
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kPaWarps = kThreads / 32;
-constexpr int kStepTokens = kPaWarps * 16;      // tokens one step of the whole CTA covers
+// Warps per CTA: 8 (two CTAs per SM, so that one CTA's table set-up and final merge overlap the other's token loop)
+// where two sets of tables fit in shared memory, 16 (one CTA per SM) for 4-bit indices.  Either way 16 warps per SM at
+// up to 128 registers per thread.
+template <int BITS> struct PAWarps { static constexpr int value = BITS == 4 ? 16 : 8; };
 constexpr int kSignTabBytes = 8 * 16 * 128;     // [nibble position][nibble value][lane]
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -114,7 +117,10 @@ struct PALayout {
     static constexpr int kSignTabOff = kPairTabBytes + kHalfTabBytes;
     static constexpr int kStageOff = kSignTabOff + kSignTabBytes;
     static constexpr int kStageBytes = 32 * kRow + 256;                 // 16 K rows, 16 V rows, 16 sign rows
-    static constexpr int kSmem = kStageOff + kPaWarps * kPaStages * kStageBytes;
+    static constexpr int kWarps = PAWarps<BITS>::value;
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kStepTokens = kWarps * 16;                     // tokens one step of the whole CTA covers
+    static constexpr int kSmem = kStageOff + kWarps * kPaStages * kStageBytes;
 };
 
 // A warp takes 16 tokens per step.  Lane (slot, quarter) = (lane >> 2, lane & 3) owns quarter `quarter` (32 dims) of
@@ -126,9 +132,10 @@ struct PALayout {
 //  * V: per token 16 look-ups of (c[i0], c[i1]) as floats, f32x2 multiply-adds into the lane's 32 accumulators.
 // Every slot runs its own online softmax (no exchange between tokens inside the loop).
 template <int BITS>
-__global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParams p) {
+__global__ void __launch_bounds__(PAWarps<BITS>::value * 32, 16 / PAWarps<BITS>::value) packed_attn_partial(const PAParams p, int n_items) {
     using LO = PALayout<BITS>;
     constexpr int ROW = LO::kRow;
+    constexpr int kPaWarps = LO::kWarps, kThreads = LO::kThreads, kStepTokens = LO::kStepTokens;
     extern __shared__ __align__(128) unsigned char pa_smem[];
     unsigned char* pair_tab = pa_smem;
     unsigned char* half_tab = pa_smem + LO::kPairTabBytes;
@@ -138,27 +145,37 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
     __shared__ __align__(16) float sacc[kPaWarps][kHeadDim];
     __shared__ float sml[kPaWarps][2];
 
-    const int bh = blockIdx.x, split = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slot = lane >> 2, quarter = lane & 3;
     const int per = (p.Sk + p.num_splits - 1) / p.num_splits;   // tokens per split (packed_attention.py:98-100)
-    const int t0 = min(split * per, p.Sk), t1 = min(t0 + per, p.Sk);
-    const int64_t base = static_cast<int64_t>(bh) * p.Sk;
-
-    // ---- asynchronous staging: per step a warp copies its 16 K rows, 16 V rows and 16 sign rows in 16-byte pieces
-    // (every row is a multiple of 16 bytes, so any token starts on a 16-byte boundary) ----
+    // the pair tables depend on the codebook only: built once, the CTA then strides over (row, split) items
+    if (tid < (1 << BITS)) scb[tid] = p.centroids[tid];
+    __syncthreads();
+    for (int e = tid; e < LO::kPairs * 32; e += kThreads) {
+        const int pr = e >> 5;
+        const float c0 = scb[pr & ((1 << BITS) - 1)], c1 = scb[pr >> BITS];
+        *reinterpret_cast<float2*>(pair_tab + e * 8) = make_float2(c0, c1);
+        *reinterpret_cast<uint32_t*>(half_tab + e * 4) = pack_half2(c0, c1);
+    }
+    // ---- item state: which (row, split) the CTA works on, and the warp's asynchronous staging of it: per step a warp
+    // copies its 16 K rows, 16 V rows and 16 sign rows in 16-byte pieces (every row is a multiple of 16 bytes, so any
+    // token starts on a 16-byte boundary) ----
     const uint32_t stage0 = smem_u32(pa_smem + LO::kStageOff + warp * kPaStages * LO::kStageBytes);
-    int tok16 = t0 + warp * 16;                                 // first token of this warp's current step
-    const uint8_t* kptr = p.k_idx + (base + tok16) * ROW + lane * 16;
-    const uint8_t* vptr = p.v_idx + (base + tok16) * ROW + lane * 16;
-    const uint8_t* sptr = p.k_signs + (base + tok16) * 16 + lane * 16;
-    int tok_issue = tok16;
-    int stage_issue = 0;
+    int bh = 0, split = 0, t1 = 0;
+    int tok16 = 0;                                              // first token of this warp's current step
+    const uint8_t *kptr = nullptr, *vptr = nullptr, *sptr = nullptr;
+    const uint16_t *knp = nullptr, *krnp = nullptr, *vnp = nullptr;
+    int tok_issue = 0, stage_issue = 0;
+    uint16_t nrm[6] = {0, 0, 0, 0, 0, 0};                       // kn, krn, vn of token A (slot); of token B (slot + 8)
+    // token row of this lane's pieces (piece c + lane of the 16 rows); 99 = the lane has no such piece
+    int piece_row[(ROW + 31) / 32];
+#pragma unroll
+    for (int c = 0; c < ROW; c += 32) piece_row[c / 32] = c + lane < ROW ? ((c + lane) * 16) / ROW : 99;
     auto issue = [&]() {
         const uint32_t dst = stage0 + stage_issue * LO::kStageBytes + lane * 16;
 #pragma unroll
-        for (int c = 0; c < ROW; c += 32) {                     // piece c + lane of the 16 rows
-            if (c + lane < ROW && tok_issue + ((c + lane) * 16) / ROW < t1) {
+        for (int c = 0; c < ROW; c += 32) {
+            if (tok_issue + piece_row[c / 32] < t1 && piece_row[c / 32] < 16) {
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * 16), "l"(kptr + c * 16) : "memory");
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16 * ROW + c * 16), "l"(vptr + c * 16) : "memory");
             }
@@ -172,14 +189,6 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
         tok_issue += kStepTokens;
         stage_issue = stage_issue + 1 == kPaStages ? 0 : stage_issue + 1;
     };
-#pragma unroll
-    for (int i = 0; i < kPaStages - 1; ++i) issue();
-
-    // norms of the first step: tokens slot and slot + 8
-    const uint16_t* knp = reinterpret_cast<const uint16_t*>(p.k_norm) + base;
-    const uint16_t* krnp = reinterpret_cast<const uint16_t*>(p.k_rnorm) + base;
-    const uint16_t* vnp = reinterpret_cast<const uint16_t*>(p.v_norm) + base;
-    uint16_t nrm[6] = {0, 0, 0, 0, 0, 0};     // kn, krn, vn of token A; of token B
     auto load_norms = [&](int tk, uint16_t (&n)[6]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -193,18 +202,43 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
             }
         }
     };
-    load_norms(tok16, nrm);
-
-    // ---- tables ----
-    if (tid < kHeadDim) sqp[tid] = __half2float(p.Qp[static_cast<int64_t>(bh) * kHeadDim + tid]) * p.corr_scale;
-    if (tid < (1 << BITS)) scb[tid] = p.centroids[tid];
-    __syncthreads();
-    for (int e = tid; e < LO::kPairs * 32; e += kThreads) {
-        const int pr = e >> 5;
-        const float c0 = scb[pr & ((1 << BITS) - 1)], c1 = scb[pr >> BITS];
-        *reinterpret_cast<float2*>(pair_tab + e * 8) = make_float2(c0, c1);
-        *reinterpret_cast<uint32_t*>(half_tab + e * 4) = pack_half2(c0, c1);
+    // Starts an item: its first copies and norms are requested here, i.e. (from the second item on) before the merge of
+    // the item just finished, so their latency is hidden behind it.
+    auto begin_item = [&](int item) {
+        bh = item / p.num_splits;
+        split = item - bh * p.num_splits;
+        const int t0 = min(split * per, p.Sk);
+        t1 = min(t0 + per, p.Sk);
+        const int64_t base = static_cast<int64_t>(bh) * p.Sk;
+        tok16 = t0 + warp * 16;
+        kptr = p.k_idx + (base + tok16) * ROW + lane * 16;
+        vptr = p.v_idx + (base + tok16) * ROW + lane * 16;
+        sptr = p.k_signs + (base + tok16) * 16 + lane * 16;
+        knp = reinterpret_cast<const uint16_t*>(p.k_norm) + base;
+        krnp = reinterpret_cast<const uint16_t*>(p.k_rnorm) + base;
+        vnp = reinterpret_cast<const uint16_t*>(p.v_norm) + base;
+        tok_issue = tok16;
+        stage_issue = 0;
+#pragma unroll
+        for (int i = 0; i < kPaStages - 1; ++i) issue();
+        load_norms(tok16, nrm);
+    };
+    int item = blockIdx.x;
+    if (item < n_items) begin_item(item);
+  while (item < n_items) {
+    // B operands: the query's quarter `quarter` as loaded (pairs of adjacent dims), in column 0 (slot 0) only
+    uint32_t qf[16];
+    {
+        const uint4* qsrc = reinterpret_cast<const uint4*>(p.Q + static_cast<int64_t>(bh) * kHeadDim + 32 * quarter);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 v = slot == 0 ? __ldg(qsrc + i) : make_uint4(0u, 0u, 0u, 0u);
+            qf[4 * i] = v.x; qf[4 * i + 1] = v.y; qf[4 * i + 2] = v.z; qf[4 * i + 3] = v.w;
+        }
     }
+    // ---- the query's sign table ----
+    if (tid < kHeadDim) sqp[tid] = __half2float(p.Qp[static_cast<int64_t>(bh) * kHeadDim + tid]) * p.corr_scale;
+    __syncthreads();
     // Sign nibble g = 2 c + h of a lane's sign word (byte c = byte `quarter` of sign word c) holds, in bit kk, the
     // sign of local dim 4 (4 h + kk) + c (stride-4 order: dim 4 i + c is bit i of word c).
     for (int e = tid; e < 8 * 16 * 32; e += kThreads) {
@@ -216,16 +250,6 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
             acc += ((v >> kk) & 1) ? x : -x;
         }
         *reinterpret_cast<float*>(sign_tab + e * 4) = acc;
-    }
-    // B operands: the query's quarter `quarter` as loaded (pairs of adjacent dims), in column 0 (slot 0) only
-    uint32_t qf[16];
-    {
-        const uint4* qsrc = reinterpret_cast<const uint4*>(p.Q + static_cast<int64_t>(bh) * kHeadDim + 32 * quarter);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 v = slot == 0 ? __ldg(qsrc + i) : make_uint4(0u, 0u, 0u, 0u);
-            qf[4 * i] = v.x; qf[4 * i + 1] = v.y; qf[4 * i + 2] = v.z; qf[4 * i + 3] = v.w;
-        }
     }
     __syncthreads();
     const uint32_t lane8 = lane * 8, lane4 = lane * 4;
@@ -323,6 +347,9 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
         __syncwarp();   // every lane has read this stage before the next step's copy may land in it
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const int64_t out_slot = static_cast<int64_t>(bh) * p.num_splits + split;   // of the item just finished
+    item += gridDim.x;
+    if (item < n_items) begin_item(item);
 
     // ---- merge the 8 slots of the warp, then the warps ----
     float M = m_run;
@@ -350,7 +377,6 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
         sml[warp][1] = L;
     }
     __syncthreads();
-    const int64_t out_slot = static_cast<int64_t>(bh) * p.num_splits + split;
     if (tid < kHeadDim) {
         float Mc = sml[0][0];
 #pragma unroll
@@ -368,6 +394,8 @@ __global__ void __launch_bounds__(kThreads, 1) packed_attn_partial(const PAParam
             p.ws_lse[out_slot * 2 + 1] = l;
         }
     }
+    __syncthreads();   // the shared partials and the sign table are free for the next item
+  }
 }
 
 __global__ void __launch_bounds__(kHeadDim) packed_attn_merge(const PAParams p) {
@@ -422,15 +450,18 @@ using namespace tq;
 
 extern "C" int tq_packed_attention_auto_splits(int BH, int Sk) {
     if (BH <= 0 || Sk <= 0) return TQ_ERR_ARG;
-    // One 512-thread CTA per SM: take the split count (at least 1024 tokens per split, at most 64 splits) whose grid
-    // fills whole waves of 148 CTAs best; a small penalty per split keeps the merge short among near-ties.
+    // Two 256-thread CTAs per SM (one 512-thread CTA for 4-bit indices: half as many per wave, so a grid that fills
+    // waves of 296 fills waves of 148 too).  Take the split count (at least 1024 tokens per split, at most 64 splits)
+    // whose grid fills whole waves best; a small penalty per split keeps the merge short among near-ties.
+    const char* env = getenv("TQ_PA_SPLIT_PENALTY");
+    const double penalty = env ? atof(env) : 0.002;
     const int max_splits = Sk / 1024 < 1 ? 1 : (Sk / 1024 > 64 ? 64 : Sk / 1024);
     int best = 1;
     double best_score = -1.0;
     for (int s = 1; s <= max_splits; ++s) {
-        const double waves = static_cast<double>(BH) * s / 148.0;
+        const double waves = static_cast<double>(BH) * s / 296.0;
         const double full = waves <= 1.0 ? 1.0 : static_cast<double>(static_cast<long long>(waves + 0.999999));
-        const double score = waves / full - 0.002 * s;
+        const double score = waves / full - penalty * s;
         if (score > best_score) {
             best_score = score;
             best = s;
@@ -457,7 +488,7 @@ extern "C" int tq_packed_attention(const void* Q, const void* Q_proj, const uint
         return TQ_ERR_ARG;
     if (num_splits <= 0) num_splits = tq_packed_attention_auto_splits(BH, Sk);
     if (num_splits > Sk) num_splits = Sk;
-    if (BH > 2147483647 / 1 || num_splits > 65535) return TQ_ERR_UNSUPPORTED;
+    if (num_splits > 65535) return TQ_ERR_UNSUPPORTED;
     if (!workspace || workspace_bytes < tq_packed_attention_workspace_bytes(BH, num_splits)) return TQ_ERR_WORKSPACE;
     PAParams p;
     p.Q = static_cast<const __half*>(Q);
@@ -476,21 +507,29 @@ extern "C" int tq_packed_attention(const void* Q, const void* Q_proj, const uint
     p.Sk = Sk;
     p.num_splits = num_splits;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const dim3 grid(BH, num_splits);
     static bool configured[64] = {false};
+    static int sm_count[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return TQ_ERR_LAUNCH;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (dev < 0 || dev >= 64) return TQ_ERR_UNSUPPORTED;
+    if (!configured[dev]) {
+        if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TQ_ERR_LAUNCH;
         if (cudaFuncSetAttribute(packed_attn_partial<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PALayout<4>::kSmem) != cudaSuccess ||
             cudaFuncSetAttribute(packed_attn_partial<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, PALayout<3>::kSmem) != cudaSuccess ||
             cudaFuncSetAttribute(packed_attn_partial<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PALayout<2>::kSmem) != cudaSuccess)
             return TQ_ERR_LAUNCH;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        configured[dev] = true;
     }
+    // persistent CTAs: as many as are resident at once, each strides over the (row, split) items
+    const int64_t items64 = static_cast<int64_t>(BH) * num_splits;
+    if (items64 > 2147483647) return TQ_ERR_UNSUPPORTED;
+    const int n_items = static_cast<int>(items64);
+    const int resident = sm_count[dev] * (bits == 4 ? 1 : 2);
+    const unsigned grid = static_cast<unsigned>(n_items < resident ? n_items : resident);
     switch (bits) {
-        case 2: packed_attn_partial<2><<<grid, kThreads, PALayout<2>::kSmem, st>>>(p); break;
-        case 3: packed_attn_partial<3><<<grid, kThreads, PALayout<3>::kSmem, st>>>(p); break;
-        case 4: packed_attn_partial<4><<<grid, kThreads, PALayout<4>::kSmem, st>>>(p); break;
+        case 2: packed_attn_partial<2><<<grid, PALayout<2>::kThreads, PALayout<2>::kSmem, st>>>(p, n_items); break;
+        case 3: packed_attn_partial<3><<<grid, PALayout<3>::kThreads, PALayout<3>::kSmem, st>>>(p, n_items); break;
+        case 4: packed_attn_partial<4><<<grid, PALayout<4>::kThreads, PALayout<4>::kSmem, st>>>(p, n_items); break;
     }
     if (cudaGetLastError() != cudaSuccess) return TQ_ERR_LAUNCH;
     packed_attn_merge<<<BH, kHeadDim, 0, st>>>(p);
