@@ -395,6 +395,7 @@ def parity_slice(wl: "Workload", outs: torch.Tensor, q_dev: torch.Tensor, layer:
     from oracle import tq_oracle as O
     from turboquant.kernels import paged_layout
     f = wl.fmt
+    seq = min(seq, wl.batch - 1)
     n_pages = int(wl.pages[seq])
     L = int(wl.lens[seq])
     g = wl.hq // wl.hkv
@@ -546,6 +547,10 @@ def measure_contiguous_api(device, peak: float) -> dict:
                                     "us": us_k, "GBps": gk, "frac_of_peak": gk / peak}
     res["compress_v_contiguous"] = {"workload": "compress_v, 3-bit, 1 048 576 fp16 rows, rotation in the kernel",
                                     "us": us_v, "GBps": gv, "frac_of_peak": gv / peak}
+    gbs, us = time_bulk_compress("turbo3", 1 << 18, 8, device)
+    res["compress_paged_256K_tokens"] = {"workload": "turbo3 compress-and-scatter of 262 144 new tokens x 8 KV heads (fp16 K/V)"
+                                                     + (", tcgen05 rotation kernel" if TC else ""),
+                                         "us": us, "GBps": gbs, "frac_of_peak": gbs / peak}
     return res
 
 
@@ -711,6 +716,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the other workloads' rows (single GPU only)")
+    ap.add_argument("--compress-kernel", default="default", choices=["default", "tcgen05"],
+                    help="rotation kernel of the bulk compress rows: mma.sync (default) or the opt-in tcgen05 / tensor-memory one")
     ap.add_argument("--micro", action="store_true",
                     help="only the contiguous-API rows (packed_attention, compress_k, compress_v): one JSON line, for small profiling runs")
     ap.add_argument("--decode-kernel", default="default", choices=["default", "tcgen05"],
@@ -719,6 +726,9 @@ def main():
     if args.warmup < 3 and args.impl == "b200" and not args.layers:
         args.warmup = 3
 
+    if args.compress_kernel == "tcgen05":
+        global TC
+        TC = True
     if args.decode_kernel == "tcgen05":
         global DECODE_FLAGS
         from turboquant.kernels import _native

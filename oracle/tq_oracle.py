@@ -367,7 +367,7 @@ def paged_decode(q_rot, q_proj, k_fields: dict, v_fields: dict, block_tables, se
 
 
 # ---------------------------------------------------------------------------
-# BASELINE config 1: the CPU round trip the reference can run itself
+# The CPU round trip the reference can run itself (turbo3 + QJL, 128-dim heads, seed 0)
 # ---------------------------------------------------------------------------
 
 

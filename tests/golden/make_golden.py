@@ -131,7 +131,7 @@ out["attn_centroids"] = cent.numpy()
 out["attn_corr_scale"] = np.float64(cs)
 out["attn_ref_out"] = ref.numpy()
 
-# --- BASELINE config 1: CPU round trip (turbo3 + QJL, seed 0) -----------------
+# --- the CPU round trip the reference can run itself (turbo3 + QJL, seed 0) -----------------
 torch.manual_seed(0)
 K = torch.randn(1024, 128)
 V = torch.randn(1024, 128)
