@@ -220,16 +220,27 @@ def permute_signs_for_chunked(signs_packed: np.ndarray, D: int = 128) -> np.ndar
     return pack_1bit(perm).reshape(shape)
 
 
-def compress_k_packed(K, centroids, boundaries, bits: int, rotation_matrix=None, permuted: bool = True):
+def compress_k_packed(K, centroids, boundaries, bits: int, rotation_matrix=None, permuted: bool = True,
+                      sign_projection=None):
     """Packed K in the contiguous format of compress_k / compress_k_permuted.
 
     Return order of turboquant/kernels/packed_compress.py:177 (k_idx, k_signs,
     k_rnorm, k_norm), arithmetic of turboquant/core/quantizer.py:111-183,
-    norms rounded to fp16 as at packed_compress.py:63,73.
+    norms rounded to fp16 as at packed_compress.py:63,73.  sign_projection
+    (PiST of packed_compress.py:75-77): the signs are those of
+    (rotated residual) @ sign_projection instead of the rotated residual's own.
     """
     r = polarquant_compress(K, centroids, boundaries, bits, True, rotation_matrix)
     k_idx = pack_indices(r["indices"], bits)
-    k_signs = pack_1bit(r["signs"] > 0)
+    if sign_projection is None:
+        positive = r["signs"] > 0
+    else:
+        x = np.asarray(K, dtype=F32).reshape(-1, np.asarray(K).shape[-1])
+        x_rot = x if rotation_matrix is None else (x @ rotation_matrix.astype(F32)).astype(F32)
+        x_n = (x_rot / (r["norms"][:, None] + F32(1e-8))).astype(F32)
+        resid = ((x_n - np.asarray(centroids, dtype=F32)[r["indices"]]) * r["norms"][:, None]).astype(F32)
+        positive = (resid @ np.asarray(sign_projection, dtype=F32)) >= 0
+    k_signs = pack_1bit(positive)
     if permuted:
         k_signs = permute_signs_for_chunked(k_signs)
     return k_idx, k_signs, r["rot_residual_norm"].astype(np.float16), r["norms"].astype(np.float16)

@@ -147,6 +147,40 @@ def test_compress_contiguous_large_tight_codebook_and_nonfinite_rows(rotate):
         assert not torch.isfinite(k_n[17].float()) and not torch.isfinite(k_n[n - 1].float())
 
 
+def test_compress_k_v_general_rotation_and_projection_matrices():
+    """The reference's own demo (packed_compress.py:247-275) passes a QR-orthogonal Pi and PiST = Pi S^T with a
+    Gaussian S.  Such matrices take the composed path (matrix products around the same quantizer kernels): indices
+    within the 1e-4 allowance of a differently rounded rotation, projected signs equal except where the projection is
+    within rounding of zero."""
+    n = 3001
+    x = _inputs(n, seed=11)
+    c, b = make_codebook(128, 2)
+    g = torch.Generator().manual_seed(3)
+    Pi, _ = torch.linalg.qr(torch.randn(128, 128, generator=g))
+    S = torch.randn(128, 128, generator=g)
+    PiT, PiST = Pi.T.contiguous(), (Pi @ S.T).contiguous()
+    for pit, pist in ((PiT, PiST), (PiT, None), (make_wht_matrix(128), PiST), (None, PiST)):
+        rot = None if pit is None else pit.numpy()
+        o_idx, o_sg, o_rn, o_n = O.compress_k_packed(x.numpy(), c.numpy(), b.numpy(), 2, rot, permuted=False,
+                                                     sign_projection=None if pist is None else pist.numpy())
+        k_idx, k_sg, k_rn, k_n = packed_compress.compress_k(x.to(DEV), None if pit is None else pit.to(DEV),
+                                                            None if pist is None else pist.to(DEV), c.to(DEV), b.to(DEV))
+        got = packed_compress.unpack_indices(k_idx.cpu(), 2).numpy()
+        want = O.unpack_indices(o_idx, 2)
+        assert (got != want).mean() <= 1e-4 and np.abs(got.astype(int) - want).max() <= 1
+        assert (np.unpackbits(k_sg.cpu().numpy(), axis=1) != np.unpackbits(o_sg, axis=1)).mean() <= 2e-4
+        assert _half_ulp_close(k_n, o_n.astype(np.float32)) and _half_ulp_close(k_rn, o_rn.astype(np.float32), max_ulp=2)
+        _, k_sgp, _, _ = packed_compress.compress_k_permuted(x.to(DEV), None if pit is None else pit.to(DEV),
+                                                            None if pist is None else pist.to(DEV), c.to(DEV), b.to(DEV))
+        assert torch.equal(packed_compress.permute_signs_for_chunked(k_sg.cpu()), k_sgp.cpu())
+    v_idx, v_n = packed_compress.compress_v(x.to(DEV), PiT.to(DEV), c.to(DEV), b.to(DEV))
+    ov_idx, ov_n = O.compress_v_packed(x.numpy(), c.numpy(), b.numpy(), 2, PiT.numpy())
+    assert (packed_compress.unpack_indices(v_idx.cpu(), 2).numpy() != O.unpack_indices(ov_idx, 2)).mean() <= 1e-4
+    assert _half_ulp_close(v_n, ov_n.astype(np.float32))
+    with pytest.raises(ValueError):
+        packed_compress.compress_v(x.to(DEV), (2 * PiT).to(DEV), c.to(DEV), b.to(DEV))      # not orthogonal
+
+
 def test_compress_empty_and_single():
     c, b = make_codebook(128, 3)
     e = torch.empty(0, 128, device=DEV)

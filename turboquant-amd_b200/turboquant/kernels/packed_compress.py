@@ -9,9 +9,15 @@ Differences from the reference that are deliberate:
     fp16-dot variant of the Triton kernel;
   * `centroids.numel()` selects the bit width (4, 8 or 16 centroids -> 2, 3,
     4 bits per index); the reference kernel is 2-bit only;
-  * PiT must be None or the Walsh-Hadamard matrix of make_wht_matrix(128);
-    PiST must be None or the identity (signs are taken of the rotated
-    residual itself, S = I, as in turboquant.core).
+  * the fused kernel applies the Walsh-Hadamard rotation of
+    make_wht_matrix(128) and takes the signs of the rotated residual itself
+    (S = I, as in turboquant.core): PiT None / that matrix and PiST None / the
+    identity select it.  Any other orthogonal PiT (the reference's own demo,
+    packed_compress.py:247-275, passes a QR-orthogonal Pi) and any PiST
+    (Pi S^T with a Gaussian S there) take a composed path: the rotation and the
+    projection of the residual are plain matrix products (torch.matmul), the
+    quantisation in between runs on the same kernels.  That path is there for
+    call compatibility, it is not a tuned one.
 """
 from __future__ import annotations
 
@@ -74,22 +80,90 @@ def _bits_of(centroids: torch.Tensor) -> int:
     return n.bit_length() - 1
 
 
+def _remembered(matrix: torch.Tensor, tag: str, test) -> bool:
+    """test(matrix), evaluated once per tensor object and content version."""
+    key = "_tq_" + tag
+    hit = getattr(matrix, key, None)
+    if hit is not None and hit[0] == matrix._version:
+        return hit[1]
+    verdict = bool(test(matrix))
+    setattr(matrix, key, (matrix._version, verdict))
+    return verdict
+
+
+def _is_wht(matrix: torch.Tensor) -> bool:
+    from turboquant.core.rotation import make_wht_matrix
+    return _remembered(matrix, "is_wht", lambda m: tuple(m.shape) == (128, 128) and torch.allclose(
+        m.detach().float().cpu(), make_wht_matrix(128), atol=1e-6, rtol=0))
+
+
+def _is_identity(matrix: torch.Tensor) -> bool:
+    return _remembered(matrix, "is_eye", lambda m: tuple(m.shape) == (128, 128) and torch.equal(
+        m.detach().float().cpu(), torch.eye(128)))
+
+
+def _is_orthogonal(matrix: torch.Tensor) -> bool:
+    def test(m):
+        mf = m.detach().float().cpu()
+        return tuple(mf.shape) == (128, 128) and (mf @ mf.T - torch.eye(128)).abs().max().item() < 1e-3
+    return _remembered(matrix, "is_orth", test)
+
+
 def _check_rotation(PiT, PiST) -> bool:
-    """True when the kernel must rotate (PiT is the WHT matrix), False when K is already rotated."""
-    if PiST is not None:
-        eye = torch.eye(128, device=PiST.device, dtype=PiST.dtype)
-        if tuple(PiST.shape) != (128, 128) or not torch.equal(PiST, eye):
-            raise ValueError("PiST must be None or the identity: signs are taken of the rotated residual (S = I)")
+    """True when the fused kernel must rotate (PiT is the WHT matrix), False when the input is already rotated.
+    Only for the fused path: PiT None / WHT, PiST None / identity."""
+    if PiST is not None and not _is_identity(PiST):
+        raise ValueError("PiST must be None or the identity on the fused path")
     if PiT is None:
         return False
     _native.check_is_wht(PiT, 128)
     return True
 
 
+def _fused_ok(PiT, PiST) -> bool:
+    return (PiT is None or _is_wht(PiT)) and (PiST is None or _is_identity(PiST))
+
+
+def _rotate_general(X: torch.Tensor, PiT: torch.Tensor) -> torch.Tensor:
+    """X @ PiT in fp32 for an orthogonal PiT that is not the WHT matrix (packed_compress.py:65-66 of the reference,
+    where the product is taken of the normalised rows; for an orthogonal matrix the norm is the same either side)."""
+    if not _is_orthogonal(PiT):
+        raise ValueError("PiT must be an orthogonal 128 x 128 matrix (the norm is taken after the rotation)")
+    return X.float() @ PiT.to(device=X.device, dtype=torch.float32)
+
+
+def _pack_sign_bytes(positive: torch.Tensor) -> torch.Tensor:
+    """[N, 128] bool -> [N, 16] uint8, byte j bit b = dim 8 j + b."""
+    w = (1 << torch.arange(8, device=positive.device, dtype=torch.int32))
+    return (positive.reshape(-1, 16, 8).to(torch.int32) * w).sum(-1).to(torch.uint8)
+
+
+def _compress_k_general(K, PiT, PiST, centroids, boundaries, permute: bool):
+    """compress_k for an orthogonal PiT other than the WHT matrix and / or a PiST other than the identity
+    (packed_compress.py:65-76 of the reference): rotate by a matrix product, quantise with the fused kernel on the
+    rotated rows, and, when PiST is given, take the signs of (rotated residual) @ PiST."""
+    from turboquant.core.quantizer import PolarQuantConfig, polarquant_compress
+    K_rot = K.float() if PiT is None else (_rotate_general(K, PiT) if not _is_wht(PiT) else None)
+    if K_rot is None:                     # WHT rotation, general PiST: rotate with the fast transform
+        K_rot = _native.wht_rows(K.float().contiguous())
+    K_rot = K_rot.contiguous()
+    k_idx, k_signs, k_rnorm, k_norm = _compress_k(K_rot, None, None, centroids, boundaries, permute=False)
+    if PiST is not None and not _is_identity(PiST):
+        bits = _bits_of(centroids)
+        r = polarquant_compress(K_rot, centroids, boundaries, PolarQuantConfig(bits=bits, use_qjl=False), None)
+        proj = (K_rot - r["k_mse_rot"]) @ PiST.to(device=K.device, dtype=torch.float32)
+        k_signs = _pack_sign_bytes(proj >= 0)
+    if permute:
+        k_signs = permute_signs_for_chunked(k_signs)
+    return k_idx, k_signs, k_rnorm, k_norm
+
+
 def _compress_k(K, PiT, PiST, centroids, boundaries, permute: bool):
     dev = _native._require_cuda(K)
     if K.dim() != 2 or K.shape[1] != 128:
         raise ValueError("K must be [N, 128]")
+    if not _fused_ok(PiT, PiST):
+        return _compress_k_general(K, PiT, PiST, centroids, boundaries, permute)
     rotate = _check_rotation(PiT, PiST)
     bits = _bits_of(centroids)
     if K.dtype not in _native._DTYPES:
@@ -125,6 +199,8 @@ def compress_v(V, PiT, centroids, boundaries):
     dev = _native._require_cuda(V)
     if V.dim() != 2 or V.shape[1] != 128:
         raise ValueError("V must be [N, 128]")
+    if PiT is not None and not _is_wht(PiT):      # an orthogonal matrix other than the WHT: rotate by a matrix product
+        return compress_v(_rotate_general(V, PiT).contiguous(), None, centroids, boundaries)
     rotate = _check_rotation(PiT, None)
     bits = _bits_of(centroids)
     if V.dtype not in _native._DTYPES:
