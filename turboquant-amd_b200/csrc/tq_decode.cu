@@ -113,13 +113,23 @@ struct DecodeParams {
 // permutes and the interleave permute of the register-only path: the logic pipe is the
 // bottleneck of this kernel, the load/store pipe is not.
 // ---------------------------------------------------------------------------------
+// 2-bit indices: a whole byte of a packed word (four indices = two pairs: bits 1:0 with 5:4, bits 3:2 with 7:6)
+// addresses a table of two half2, so one look-up serves four elements; an entry holds 16 copies of its 8 bytes (a 64-bit
+// load is served half a warp at a time, lanes l and l + 16 never meet).
 template <int BITS>
-__host__ __device__ constexpr int lut_entries() { return BITS == 2 ? 64 : (BITS == 3 ? 128 : 256); }
+__host__ __device__ constexpr int lut_entries() { return BITS == 2 ? 256 : (BITS == 3 ? 128 : 256); }
 template <int BITS>
 __host__ __device__ constexpr int lut_bytes() { return lut_entries<BITS>() * 128; }
 
 template <int BITS>
 __device__ __forceinline__ void fill_pair_lut(uint32_t* tab, const float* __restrict__ c, int warp, int lane) {
+    if constexpr (BITS == 2) {
+        for (int b = warp; b < 256; b += kWarps) {
+            const int i0 = (lane & 1) ? (b >> 2) & 3 : b & 3, i1 = (lane & 1) ? (b >> 6) & 3 : (b >> 4) & 3;   // word 0: pair A, word 1: pair B
+            tab[b * 32 + lane] = pack_half2(__half2float(__float2half_rn(__ldg(c + i0))), __half2float(__float2half_rn(__ldg(c + i1))));
+        }
+        return;
+    }
     for (int b = warp; b < lut_entries<BITS>(); b += kWarps) {
         const int i0 = b & 15, i1 = b >> 4;
         if (i0 < (1 << BITS) && i1 < (1 << BITS))
@@ -151,6 +161,15 @@ __device__ __forceinline__ uint32_t lut_pair(uint32_t lane_base, uint32_t mw, in
     const uint32_t x = prmt(mw, 0u, 0x4440u | static_cast<uint32_t>(k));
     uint32_t v;
     asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lane_base + x * 128u));
+    return v;
+}
+
+// 2-bit tables: (half2 of the pair in bits 1:0 / 5:4, half2 of the pair in bits 3:2 / 7:6) for byte k of a packed
+// word; lane_base = shared address of the table + 8 * (lane & 15).
+__device__ __forceinline__ uint2 lut_quad(uint32_t lane_base, uint32_t w, int k) {
+    const uint32_t x = prmt(w, 0u, 0x4440u | static_cast<uint32_t>(k));
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(lane_base + x * 128u));
     return v;
 }
 
@@ -402,7 +421,8 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
     fill_pair_lut<KB>(tabk, p.kc, warp, lane);
     if (!p.share_tables) fill_pair_lut<VB>(tabv, p.vc, warp, lane);
     __syncthreads();
-    const uint32_t klut = smem_u32(tabk) + 4 * lane, vlut = smem_u32(tabv) + 4 * lane;
+    const uint32_t klut = smem_u32(tabk) + (KB == 2 ? 8 * (lane & 15) : 4 * lane);
+    const uint32_t vlut = smem_u32(tabv) + (VB == 2 ? 8 * (lane & 15) : 4 * lane);
     // this lane's three access patterns inside a ring stage: its two K records, the norm slots, the V words
     const uint32_t ring_k = smem_u32(myring) + lane * (NWK * 4);
     const uint32_t ring_n = smem_u32(myring) + gid * 4;
@@ -444,14 +464,27 @@ __global__ void __launch_bounds__(kThreads, TQ_DEC_MINBLOCKS) decode_partial_ker
 #pragma unroll
             for (int i = 0; i < VB; ++i)
                 pw[i] = i == 0 ? lds_u32<KPART>(vo) : (i == 1 ? lds_u32<KPART + 256>(vo) : (i == 2 ? lds_u32<KPART + 512>(vo) : lds_u32<KPART + 768>(vo)));
-            uint32_t mv[4];
-            masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
+            if constexpr (VB == 2) {
+                // byte k of packed word jw: the pairs of group u = 2 jw (first half2) and u = 2 jw + 1 (second)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t a0 = lut_pair(vlut, mv[u], 0), a1 = lut_pair(vlut, mv[u], 1);
-                const uint32_t b0 = lut_pair(vlut, mv[u], 2), b1 = lut_pair(vlut, mv[u], 3);
-                mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
-                mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
+                for (int jw = 0; jw < 2; ++jw) {
+                    const uint2 a0 = lut_quad(vlut, pw[jw], 0), a1 = lut_quad(vlut, pw[jw], 1);
+                    const uint2 b0 = lut_quad(vlut, pw[jw], 2), b1 = lut_quad(vlut, pw[jw], 3);
+                    mma_f16_16816(oacc[4 * jw], pa0, pa1, pa2, pa3, a0.x, b0.x);
+                    mma_f16_16816(oacc[4 * jw + 1], pa0, pa1, pa2, pa3, a1.x, b1.x);
+                    mma_f16_16816(oacc[4 * jw + 2], pa0, pa1, pa2, pa3, a0.y, b0.y);
+                    mma_f16_16816(oacc[4 * jw + 3], pa0, pa1, pa2, pa3, a1.y, b1.y);
+                }
+            } else {
+                uint32_t mv[4];
+                masked_words<VB>(pw, mv);   // bytes 0,1: token a (dims 4u..4u+3), bytes 2,3: token b
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t a0 = lut_pair(vlut, mv[u], 0), a1 = lut_pair(vlut, mv[u], 1);
+                    const uint32_t b0 = lut_pair(vlut, mv[u], 2), b1 = lut_pair(vlut, mv[u], 3);
+                    mma_f16_16816(oacc[2 * u], pa0, pa1, pa2, pa3, a0, b0);
+                    mma_f16_16816(oacc[2 * u + 1], pa0, pa1, pa2, pa3, a1, b1);
+                }
             }
         }
     };
