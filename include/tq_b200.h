@@ -187,7 +187,11 @@ int tq_wht_rows(const void* in, void* out, int dtype, int64_t n_rows, float scal
  * turboquant/kernels/sparse_v.py:57-60), k_signs uint8 [n, 16] (sequential,
  * or in the stride-4 order of permute_signs_for_chunked,
  * packed_compress.py:180-216, when permute_signs), k_rnorm and k_norm fp16 [n].
- * Arithmetic as turboquant/core/quantizer.py:141-173. */
+ * Arithmetic as turboquant/core/quantizer.py:141-173.  More than 16384 rows
+ * take the persistent table-driven kernel (as tq_compress_paged: on already
+ * rotated rows the indices and signs are the reference's bit for bit, with
+ * the rotation done here at most 1e-4 of the coordinates differ by one
+ * centroid); smaller launches take the binary-search kernel. */
 int tq_compress_k(const void* K, int in_dtype, int64_t n, const float* centroids, const float* boundaries,
                   int bits, int prerotated, int permute_signs,
                   uint8_t* k_idx, uint8_t* k_signs, void* k_rnorm, void* k_norm, tq_stream_t stream);
