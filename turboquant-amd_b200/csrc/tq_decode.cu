@@ -121,19 +121,22 @@ __host__ __device__ constexpr int lut_entries() { return BITS == 2 ? 256 : (BITS
 template <int BITS>
 __host__ __device__ constexpr int lut_bytes() { return lut_entries<BITS>() * 128; }
 
+// Every lane fetches one centroid (already rounded to fp16) and the entries are assembled from warp shuffles, so the
+// fill does not wait on a global load per entry.
 template <int BITS>
 __device__ __forceinline__ void fill_pair_lut(uint32_t* tab, const float* __restrict__ c, int warp, int lane) {
+    const float cv = __half2float(__float2half_rn(__ldg(c + (lane & ((1 << BITS) - 1)))));
     if constexpr (BITS == 2) {
         for (int b = warp; b < 256; b += kWarps) {
             const int i0 = (lane & 1) ? (b >> 2) & 3 : b & 3, i1 = (lane & 1) ? (b >> 6) & 3 : (b >> 4) & 3;   // word 0: pair A, word 1: pair B
-            tab[b * 32 + lane] = pack_half2(__half2float(__float2half_rn(__ldg(c + i0))), __half2float(__float2half_rn(__ldg(c + i1))));
+            tab[b * 32 + lane] = pack_half2(__shfl_sync(0xffffffffu, cv, i0), __shfl_sync(0xffffffffu, cv, i1));
         }
         return;
     }
     for (int b = warp; b < lut_entries<BITS>(); b += kWarps) {
         const int i0 = b & 15, i1 = b >> 4;
-        if (i0 < (1 << BITS) && i1 < (1 << BITS))
-            tab[b * 32 + lane] = pack_half2(__half2float(__float2half_rn(__ldg(c + i0))), __half2float(__float2half_rn(__ldg(c + i1))));
+        const float c0 = __shfl_sync(0xffffffffu, cv, i0 & ((1 << BITS) - 1)), c1 = __shfl_sync(0xffffffffu, cv, i1 & ((1 << BITS) - 1));
+        if (i0 < (1 << BITS) && i1 < (1 << BITS)) tab[b * 32 + lane] = pack_half2(c0, c1);
     }
 }
 
