@@ -17,8 +17,6 @@
 //    maximum is only raised when a score exceeds it by 2^8); slots, warps and splits are merged at the end.
 #include "tq_common.cuh"
 
-#include <cstdlib>
-
 namespace tq {
 namespace {
 
@@ -453,8 +451,7 @@ extern "C" int tq_packed_attention_auto_splits(int BH, int Sk) {
     // Two 256-thread CTAs per SM (one 512-thread CTA for 4-bit indices: half as many per wave, so a grid that fills
     // waves of 296 fills waves of 148 too).  Take the split count (at least 1024 tokens per split, at most 64 splits)
     // whose grid fills whole waves best; a small penalty per split keeps the merge short among near-ties.
-    const char* env = getenv("TQ_PA_SPLIT_PENALTY");
-    const double penalty = env ? atof(env) : 0.002;
+    const double penalty = 0.002;
     const int max_splits = Sk / 1024 < 1 ? 1 : (Sk / 1024 > 64 ? 64 : Sk / 1024);
     int best = 1;
     double best_score = -1.0;
