@@ -187,7 +187,7 @@ int tq_wht_rows(const void* in, void* out, int dtype, int64_t n_rows, float scal
  * turboquant/kernels/sparse_v.py:57-60), k_signs uint8 [n, 16] (sequential,
  * or in the stride-4 order of permute_signs_for_chunked,
  * packed_compress.py:180-216, when permute_signs), k_rnorm and k_norm fp16 [n].
- * Arithmetic as turboquant/core/quantizer.py:141-173.  More than 16384 rows
+ * Arithmetic as turboquant/core/quantizer.py:141-173.  More than 32768 rows
  * take the persistent table-driven kernel (as tq_compress_paged: on already
  * rotated rows the indices and signs are the reference's bit for bit, with
  * the rotation done here at most 1e-4 of the coordinates differ by one

@@ -83,7 +83,7 @@ def test_polarquant_dict_contract():
         polarquant_compress(x, c.to(DEV), b.to(DEV), PolarQuantConfig(bits=3), torch.eye(128, device=DEV))
 
 
-@pytest.mark.parametrize("n", [4099, 16805])   # generic kernel / persistent table-driven kernel (more than 16384 rows); both ragged
+@pytest.mark.parametrize("n", [4099, 33189])   # generic kernel / persistent table-driven kernel (more than 32768 rows); both ragged
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 def test_compress_k_v_contiguous_vs_oracle(bits, dtype, n):
@@ -122,9 +122,9 @@ def test_compress_k_v_contiguous_vs_oracle(bits, dtype, n):
 
 @pytest.mark.parametrize("rotate", [False, True])
 def test_compress_contiguous_large_tight_codebook_and_nonfinite_rows(rotate):
-    """More than 16384 rows take the persistent kernel.  A codebook with two boundaries closer than 1/64 makes it fall
+    """More than 32768 rows take the persistent kernel.  A codebook with two boundaries closer than 1/64 makes it fall
     back to the binary search inside the kernel; a NaN / Inf row spoils only itself."""
-    n = 16805
+    n = 33189
     x = _inputs(n, seed=5).half()
     x[17, 5] = float("nan")
     x[n - 1, 100] = float("inf")
