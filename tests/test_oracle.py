@@ -161,3 +161,23 @@ def test_paged_decode_matches_dense_formula():
     out1, st = O.paged_decode(q, q, kf, vf, bt, lens, kc, kc, sm, cs, bs, sparse_thresh=1e-6, return_stats=True)
     assert st["positions"] == int(lens.sum()) * Hkv
     assert np.abs(out1 - out).max() <= 1e-4
+
+
+def test_compress_k_packed_sign_projection():
+    """The projected signs (PiST of turboquant/kernels/packed_compress.py:75-77): the identity projection gives the
+    residual's own signs, a general projection the signs of residual @ PiST computed from the unpacked fields."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((64, 128)).astype(np.float32)
+    c, b = O.make_codebook(128, 2)
+    H = O.make_wht_matrix(128)
+    base = O.compress_k_packed(x, c, b, 2, H, permuted=False)
+    eye = O.compress_k_packed(x, c, b, 2, H, permuted=False, sign_projection=np.eye(128, dtype=np.float32))
+    assert all(np.array_equal(u, v) for u, v in zip(base, eye))
+    S = rng.standard_normal((128, 128)).astype(np.float32)
+    proj = O.compress_k_packed(x, c, b, 2, H, permuted=False, sign_projection=S)
+    r = O.polarquant_compress(x, c, b, 2, True, H)
+    resid = (x @ H).astype(np.float32) - r["k_mse_rot"]
+    want = (resid @ S) >= 0
+    got = np.unpackbits(proj[1], axis=1, bitorder="little").astype(bool)
+    assert (got != want).mean() <= 1e-3          # the two residual formulas differ by rounding only
+    assert np.array_equal(proj[0], base[0]) and np.array_equal(proj[3], base[3])
